@@ -1,0 +1,300 @@
+"""The cache manager: slots, page groups, block tables and per-request state.
+
+Requests live in *slots*.  Caches with a growing need (keys and values) are
+kept in pages.  Caches whose need for pages is the same (all tokens, or a
+window of W tokens) form a *group*: a group has one pool of page ids and one
+block table per slot, and a page id is valid in the storage of every cache of
+its group.  Caches of fixed size per request (`SlotStateNeed`) are rows of a
+tensor indexed by slot.
+
+Bookkeeping follows the reference's `DecodeState`
+(simply/utils/ragged_paged_attention.py:176-541), moved to the host:
+
+* `extend` = `release_for_window().allocate(q_lens)` (:437-518): before a step,
+  a windowed group gives back the pages that lie wholly below what the step's
+  first query can see, then every group takes the pages the new tokens need.
+  The count of pages to give back is `max(len - (W-1), 0) // page_size`, the
+  reference's `max(kv_len - window_size, 0) // page_size` with its
+  `window_size = W - 1` (:437-443).
+* groups: the reference shares bookkeeping between layers with equal
+  `(total_pages, page_size, window)` (:865-867, :901-917).
+* `release_slot` = `release` (:521-541).
+
+Unlike the reference the block table is indexed by the absolute page number of
+a position (`position // page_size`); pages that were given back read -1.  The
+kernels never follow a -1.  A step that cannot get its pages raises
+`OutOfPages` before anything is changed (the reference leaves that case
+undefined, :493-494).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Mapping, Sequence
+
+import numpy as np
+import torch
+
+from simply_b200.cache.needs import PagedKVNeed, SlotStateNeed
+from simply_b200.cache.page_pool import OutOfPages, PagePool
+
+
+def _cdiv(a: int, b: int) -> int:
+  return -(-a // b)
+
+
+class PageGroup:
+  """Pages and block tables of the caches that share one window."""
+
+  def __init__(self, window: int | None, page_size: int, num_pages: int, max_slots: int,
+               max_seq_len: int):
+    self.window = window
+    self.page_size = page_size
+    self.pool = PagePool(num_pages)
+    self.max_pages_per_seq = _cdiv(max_seq_len, page_size)
+    self.tables = np.full((max_slots, self.max_pages_per_seq), -1, dtype=np.int32)
+    # Pages [first_page, end_page) of a slot are held.
+    self.first_page = np.zeros(max_slots, dtype=np.int64)
+    self.end_page = np.zeros(max_slots, dtype=np.int64)
+    self.cache_names: list[str] = []
+
+  def plan(self, slot: int, cur_len: int, n_new: int) -> tuple[int, int]:
+    """(pages to give back, pages to take) for `n_new` tokens after `cur_len` cached ones."""
+    first, end = int(self.first_page[slot]), int(self.end_page[slot])
+    new_first = first
+    if self.window is not None:
+      new_first = max(first, max(cur_len - (self.window - 1), 0) // self.page_size)
+      new_first = min(new_first, end)
+    new_end = max(end, _cdiv(cur_len + n_new, self.page_size))
+    return new_first - first, new_end - end
+
+  def apply(self, slot: int, cur_len: int, n_new: int) -> tuple[list[int], list[int]]:
+    """Carries out `plan`; returns (pages given back, pages taken)."""
+    n_back, n_take = self.plan(slot, cur_len, n_new)
+    first, end = int(self.first_page[slot]), int(self.end_page[slot])
+    row = self.tables[slot]
+    back = [int(p) for p in row[first:first + n_back]]
+    self.pool.give_back(back)
+    row[first:first + n_back] = -1
+    self.first_page[slot] = first + n_back
+    taken = self.pool.take(n_take)
+    row[end:end + n_take] = taken
+    self.end_page[slot] = end + n_take
+    return back, taken
+
+  def release_slot(self, slot: int) -> list[int]:
+    first, end = int(self.first_page[slot]), int(self.end_page[slot])
+    back = [int(p) for p in self.tables[slot, first:end]]
+    self.pool.give_back(back)
+    self.tables[slot, :] = -1
+    self.first_page[slot] = 0
+    self.end_page[slot] = 0
+    return back
+
+  def held_pages(self, slot: int) -> list[int]:
+    return [int(p) for p in self.tables[slot, int(self.first_page[slot]):int(self.end_page[slot])]]
+
+
+@dataclasses.dataclass
+class PagedCache:
+  """Handle a mixer gets for its paged cache."""
+
+  name: str
+  group: int  # index into CacheManager.groups
+  need: PagedKVNeed
+  # [num_pages, 2 (keys, values), num_kv_heads, page_size, head_dim]
+  storage: torch.Tensor | None
+
+
+@dataclasses.dataclass
+class SlotState:
+  """Handle a mixer gets for its per-request state: tensor [max_slots, *shape]."""
+
+  name: str
+  need: SlotStateNeed
+  storage: torch.Tensor | None
+
+
+class CacheManager:
+
+  def __init__(
+      self,
+      needs: Mapping[str, PagedKVNeed | SlotStateNeed | None],
+      *,
+      page_size: int,
+      max_slots: int,
+      max_seq_len: int,
+      max_cache_tokens: int,
+      dtype: torch.dtype = torch.float32,
+      device: torch.device | str | None = "cpu",
+      poison_freed_pages: bool = False,
+  ):
+    """`device=None` keeps the books only (no storage), for host-side tests."""
+    self.page_size = page_size
+    self.max_slots = max_slots
+    self.max_seq_len = max_seq_len
+    self.num_pages = _cdiv(max_cache_tokens, page_size)
+    self.poison_freed_pages = poison_freed_pages
+    self.groups: list[PageGroup] = []
+    self.paged: dict[str, PagedCache] = {}
+    self.states: dict[str, SlotState] = {}
+    group_of_window: dict[int | None, int] = {}
+    for name, need in needs.items():
+      if need is None:
+        continue
+      if isinstance(need, PagedKVNeed):
+        if need.window is not None and need.window <= 0:
+          raise ValueError(f"cache {name!r}: window must be positive, got {need.window}")
+        g = group_of_window.get(need.window)
+        if g is None:
+          g = len(self.groups)
+          group_of_window[need.window] = g
+          self.groups.append(
+              PageGroup(need.window, page_size, self.num_pages, max_slots, max_seq_len))
+        self.groups[g].cache_names.append(name)
+        storage = None
+        if device is not None:
+          storage = torch.zeros(
+              (self.num_pages, 2, need.num_kv_heads, page_size, need.head_dim),
+              dtype=dtype, device=device)
+        self.paged[name] = PagedCache(name, g, need, storage)
+      elif isinstance(need, SlotStateNeed):
+        storage = None
+        if device is not None:
+          storage = torch.zeros((max_slots, *need.shape), dtype=getattr(torch, need.dtype),
+                                device=device)
+        self.states[name] = SlotState(name, need, storage)
+      else:
+        raise TypeError(f"cache {name!r}: unknown kind of need {need!r}")
+    self.lengths = np.zeros(max_slots, dtype=np.int64)
+    self.owner: list[object | None] = [None] * max_slots
+    self._free_slots = list(range(max_slots - 1, -1, -1))
+
+  # ---- slots ----------------------------------------------------------------
+  @property
+  def num_free_slots(self) -> int:
+    return len(self._free_slots)
+
+  def acquire_slot(self, owner: object) -> int:
+    if not self._free_slots:
+      raise RuntimeError("no free slot")
+    slot = self._free_slots.pop()
+    self.owner[slot] = owner
+    self.lengths[slot] = 0
+    for s in self.states.values():
+      if s.storage is not None:
+        s.storage[slot].zero_()
+    return slot
+
+  def release_slot(self, slot: int) -> None:
+    """Gives back every page of the slot and frees the slot."""
+    if self.owner[slot] is None:
+      raise ValueError(f"slot {slot} is released twice")
+    for gi, g in enumerate(self.groups):
+      self._poison(gi, g.release_slot(slot))
+    self.owner[slot] = None
+    self.lengths[slot] = 0
+    self._free_slots.append(slot)
+
+  def length(self, slot: int) -> int:
+    return int(self.lengths[slot])
+
+  # ---- pages ----------------------------------------------------------------
+  def pages_short(self, entries: Sequence[tuple[int, int]]) -> int:
+    """How many pages the batch `[(slot, new tokens)]` lacks (0 if it fits), worst group."""
+    short = 0
+    for g in self.groups:
+      back = take = 0
+      for slot, n in entries:
+        b, t = g.plan(slot, int(self.lengths[slot]), n)
+        back += b
+        take += t
+      short = max(short, take - back - g.pool.num_free)
+    return max(short, 0)
+
+  def pages_needed(self, slot: int, n_new: int) -> int:
+    """Net pages (taken minus given back) that `n_new` more tokens cost, worst group."""
+    worst = 0
+    for g in self.groups:
+      b, t = g.plan(slot, int(self.lengths[slot]), n_new)
+      worst = max(worst, t - b)
+    return worst
+
+  def min_free_pages(self) -> int:
+    return min((g.pool.num_free for g in self.groups), default=1 << 30)
+
+  def extend(self, entries: Sequence[tuple[int, int]]) -> None:
+    """Makes room for the step's new tokens; all or nothing."""
+    seen = set()
+    for slot, n in entries:
+      if self.owner[slot] is None:
+        raise ValueError(f"slot {slot} is not in use")
+      if slot in seen:
+        raise ValueError(f"slot {slot} appears twice in one step")
+      seen.add(slot)
+      if n <= 0:
+        raise ValueError(f"slot {slot}: a step entry needs at least one token, got {n}")
+      if self.lengths[slot] + n > self.max_seq_len:
+        raise ValueError(
+            f"slot {slot}: {int(self.lengths[slot])} + {n} tokens exceed max_seq_len "
+            f"{self.max_seq_len}")
+    short = self.pages_short(entries)
+    if short:
+      raise OutOfPages(f"the step lacks {short} page(s)")
+    for gi, g in enumerate(self.groups):
+      # Every slot gives back before any slot takes, as the pool may need those pages.
+      for slot, n in entries:
+        cur = int(self.lengths[slot])
+        n_back, _ = g.plan(slot, cur, 0)
+        if n_back:
+          back, _ = g.apply(slot, cur, 0)
+          self._poison(gi, back)
+      for slot, n in entries:
+        g.apply(slot, int(self.lengths[slot]), n)
+    for slot, n in entries:
+      self.lengths[slot] += n
+
+  def _poison(self, group: int, pages: list[int]) -> None:
+    if not self.poison_freed_pages or not pages:
+      return
+    for name in self.groups[group].cache_names:
+      st = self.paged[name].storage
+      if st is not None:
+        st[torch.as_tensor(pages, device=st.device, dtype=torch.long)] = float("nan")
+
+  # ---- checks ---------------------------------------------------------------
+  def check_invariants(self) -> None:
+    """No page lost, none held twice, tables and lengths consistent."""
+    for g in self.groups:
+      held: list[int] = []
+      for slot in range(self.max_slots):
+        pages = g.held_pages(slot)
+        if self.owner[slot] is None and pages:
+          raise AssertionError(f"free slot {slot} holds pages {pages}")
+        if any(p < 0 for p in pages):
+          raise AssertionError(f"slot {slot} holds an invalid page id in {pages}")
+        row = g.tables[slot]
+        outside = np.concatenate([row[:int(g.first_page[slot])], row[int(g.end_page[slot]):]])
+        if (outside != -1).any():
+          raise AssertionError(f"slot {slot} has page ids outside its held range")
+        if self.owner[slot] is not None:
+          length = int(self.lengths[slot])
+          if int(g.end_page[slot]) != _cdiv(length, self.page_size):
+            raise AssertionError(
+                f"slot {slot}: {int(g.end_page[slot])} pages end for {length} tokens")
+          if g.window is None and g.first_page[slot] != 0:
+            raise AssertionError(f"slot {slot}: a group without window gave pages back")
+          if g.window is not None and length > 0:
+            # Everything the last cached token can see must still be held.
+            oldest_visible = max(length - g.window, 0)
+            if int(g.first_page[slot]) > oldest_visible // self.page_size:
+              raise AssertionError(f"slot {slot}: pages inside the window were given back")
+        held.extend(pages)
+      free = g.pool.free_pages()
+      if len(set(held)) != len(held):
+        raise AssertionError("a page is held twice")
+      if set(held) & set(free):
+        raise AssertionError("a page is both held and free")
+      if len(held) + len(free) != g.pool.num_pages or len(set(free)) != len(free):
+        raise AssertionError(
+            f"pages lost: {len(held)} held + {len(free)} free != {g.pool.num_pages}")

@@ -1,0 +1,195 @@
+"""The engine: model + cache + step function, and generation on top of the scheduler.
+
+`step_raw` is the one step function: it takes a batch of (request slot, its next
+tokens, wanted places), makes room in the cache, runs exactly those tokens as
+one ragged batch through the model and returns float32 logits at the wanted
+places.  Generation (`generate`, `add_request` + `step`) and trace replay both
+go through it.
+
+Reference counterparts: `SamplingState.mixed_step`
+(simply/utils/ragged_paged_attention.py:1954-2062) is one step; `Batcher.loop`
+(simply/serving/page_batcher.py:701-895) and `LMInterface.generate`
+(simply/model_lib.py:4662-4942) are the loops above it.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+
+from simply_b200.cache.manager import CacheManager
+from simply_b200.config import EngineConfig, load_config
+from simply_b200.engine.batch import StepContext, StepEntry, pack_step
+from simply_b200.engine.scheduler import Request, Scheduler, StepPlan
+from simply_b200.parts.model import DecoderModel
+from simply_b200.sampling.params import SamplingParams
+from simply_b200.weights.loader import load_tensors
+from simply_b200.weights.random_init import random_tensors
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclasses.dataclass
+class GenerationResult:
+  """What `generate` returns per prompt, after the reference's `SamplingOutput`
+  (simply/model_lib.py:4459-4480): output tokens and whether the output was cut short."""
+
+  request_id: object
+  input_token_ids: list[int]
+  output_token_ids: list[int]
+  finish_reason: str
+  num_preemptions: int = 0
+
+  @property
+  def is_truncated(self) -> bool:
+    return self.finish_reason != "eos"
+
+
+def default_ops(dtype: torch.dtype):
+  """The CUDA kernel table; fails loudly when there is no GPU or the extension cannot be built."""
+  from simply_b200.kernels.ops import CudaOps
+  return CudaOps(dtype)
+
+
+class Engine:
+
+  def __init__(self, config: Any, tensors: dict[str, torch.Tensor],
+               engine_config: EngineConfig | None = None, *, ops: Any = None,
+               device: torch.device | str | None = None):
+    self.config = config
+    spec = config.model_spec()
+    self.engine_config = (engine_config or EngineConfig()).resolved(spec.max_context)
+    self.dtype = _TORCH_DTYPE[self.engine_config.activation_dtype]
+    self.ops = ops if ops is not None else default_ops(self.dtype)
+    if device is None:
+      device = "cuda" if ops is None else next(iter(tensors.values())).device
+    self.device = torch.device(device)
+    self.model = DecoderModel(spec)
+    self.model.bind(tensors, self.ops)
+    ec = self.engine_config
+    self.cache = CacheManager(
+        self.model.cache_needs(), page_size=ec.page_size, max_slots=ec.batch_size,
+        max_seq_len=ec.max_seq_len, max_cache_tokens=ec.max_cache_tokens, dtype=self.dtype,
+        device=self.device, poison_freed_pages=ec.poison_freed_pages)
+    self.caches = {**self.cache.paged, **self.cache.states}
+    eos = getattr(config, "eos_token_id", None)
+    eos_ids = () if eos is None else (tuple(eos) if isinstance(eos, (tuple, list)) else (eos,))
+    self.scheduler = Scheduler(self.cache, max_num_issue_tokens=ec.max_num_issue_tokens,
+                               max_seq_len=ec.max_seq_len, eos_ids=eos_ids)
+    self._next_id = 0
+    self.num_steps = 0
+
+  # ---- construction ---------------------------------------------------------
+  @classmethod
+  def from_folder(cls, model_dir: str, engine_config: EngineConfig | None = None, *,
+                  ops: Any = None, device: torch.device | str | None = None) -> "Engine":
+    """A model folder (config.json + *.safetensors) -> engine."""
+    config = load_config(model_dir)
+    ec = engine_config or EngineConfig()
+    dtype = _TORCH_DTYPE[ec.activation_dtype]
+    if device is None:
+      device = "cuda" if ops is None else "cpu"
+    if ops is None:
+      ops = default_ops(dtype)
+    tensors = load_tensors(model_dir, DecoderModel(config.model_spec()).tensor_specs(), dtype, device)
+    return cls(config, tensors, ec, ops=ops, device=device)
+
+  @classmethod
+  def from_config(cls, config: Any, seed: int, engine_config: EngineConfig | None = None, *,
+                  matrix_std: float = 0.02, scale_std: float = 0.0, ops: Any = None,
+                  device: torch.device | str | None = None) -> "Engine":
+    """Random weights drawn on the device, without a model folder in between."""
+    ec = engine_config or EngineConfig()
+    dtype = _TORCH_DTYPE[ec.activation_dtype]
+    if device is None:
+      device = "cuda" if ops is None else "cpu"
+    if ops is None:
+      ops = default_ops(dtype)
+    tensors = random_tensors(DecoderModel(config.model_spec()).tensor_specs(), seed,
+                             matrix_std=matrix_std, scale_std=scale_std, dtype=dtype, device=device)
+    return cls(config, tensors, ec, ops=ops, device=device)
+
+  # ---- the step function ------------------------------------------------------
+  def open_request(self, owner: object = None) -> int:
+    """Takes a slot for a request that will be stepped by hand (replay); returns the slot."""
+    return self.cache.acquire_slot(owner if owner is not None else object())
+
+  def close_request(self, slot: int) -> None:
+    self.cache.release_slot(slot)
+
+  def step_raw(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+    """Runs one batch; returns float32 logits [wanted, vocab] (None if nothing is wanted)."""
+    ctx = self._prepare(entries)
+    logits = self.model.forward(ctx, self.caches)
+    self.num_steps += 1
+    return logits
+
+  def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    vocab = self.model.spec.vocab_size
+    for e in entries:
+      for t in e.tokens:
+        if not 0 <= int(t) < vocab:
+          raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+    lengths = [self.cache.length(e.slot) for e in entries]
+    self.cache.extend([(e.slot, len(e.tokens)) for e in entries])
+    return pack_step(entries, lengths, [g.tables for g in self.cache.groups],
+                     self.cache.page_size, self.ops, self.device)
+
+  # ---- generation -------------------------------------------------------------
+  def add_request(self, prompt: Sequence[int], params: SamplingParams | None = None,
+                  request_id: object = None) -> Request:
+    if request_id is None:
+      request_id = self._next_id
+      self._next_id += 1
+    return self.scheduler.add(request_id, prompt, params or SamplingParams())
+
+  def cancel(self, request_id: object) -> bool:
+    return self.scheduler.cancel(request_id)
+
+  def has_unfinished(self) -> bool:
+    return self.scheduler.has_unfinished()
+
+  def step(self) -> list[Request]:
+    """Schedules, runs and samples one step; returns the requests that ended in it."""
+    plan = self.scheduler.schedule()
+    finished = list(plan.failed)
+    if not plan.entries:
+      return finished
+    entries = []
+    samplers = []
+    for e in plan.entries:
+      r = e.request
+      toks = r.tokens[r.num_cached:r.num_cached + e.num_tokens]
+      entries.append(StepEntry(r.slot, toks, (e.num_tokens - 1,) if e.samples else ()))
+      if e.samples:
+        samplers.append(r)
+    logits = self.step_raw(entries)
+    sampled: dict[object, int] = {}
+    if samplers:
+      tokens = self.ops.sample(
+          logits,
+          [r.params.temperature for r in samplers],
+          [r.params.top_k for r in samplers],
+          [r.params.top_p for r in samplers],
+          [r.params.seed for r in samplers],
+          [len(r.tokens) for r in samplers])
+      for r, t in zip(samplers, tokens.tolist()):
+        sampled[r.request_id] = t
+    return finished + self.scheduler.commit(plan, sampled)
+
+  def generate(self, prompts: Sequence[Sequence[int]],
+               params: SamplingParams | Sequence[SamplingParams] | None = None
+               ) -> list[GenerationResult]:
+    """Generates for every prompt (token ids in, token ids out), batching them continuously."""
+    if params is None or isinstance(params, SamplingParams):
+      params = [params or SamplingParams()] * len(prompts)
+    if len(params) != len(prompts):
+      raise ValueError(f"{len(prompts)} prompts but {len(params)} sampling parameter sets")
+    requests = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+    while self.has_unfinished():
+      self.step()
+    return [GenerationResult(r.request_id, r.prompt, r.output, r.finish_reason, r.num_preemptions)
+            for r in requests]
