@@ -1,0 +1,382 @@
+// Row-wise and element-wise kernels: embedding, norms fused with the residual add,
+// rotation tables, rotation + query scale + cache write, gated activation.
+//
+// Formulas (file:line in google-deepmind/simply):
+//   embedding            simply/utils/module.py:450-481
+//   RMS norm, (1 + w)    simply/model_lib.py:154-178
+//   block order          simply/model_lib.py:2659-2708
+//   rotation             simply/utils/position_encoding.py:83-110
+//   query scale          simply/model_lib.py:2014-2019
+//   gated activation     simply/model_lib.py:93-96, 722-726
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: out[t, :] = table[ids[t], :] * scale, float32 out (start of the residual stream).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float scale,
+                             float* __restrict__ out, int width, int vocab, int* err) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_TOKEN);
+    id = 0;
+  }
+  const T* row = table + (size_t)id * width;
+  float* o = out + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
+}
+
+extern "C" int sb_embed(const void* table, int table_dtype, const int* ids, float scale, float* out,
+                        int num_tokens, int width, int vocab, int* err, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (table_dtype == SB_DTYPE_F32)
+    embed_kernel<float><<<num_tokens, 256, 0, stream>>>((const float*)table, ids, scale, out, width, vocab, err);
+  else
+    embed_kernel<bf16><<<num_tokens, 256, 0, stream>>>((const bf16*)table, ids, scale, out, width, vocab, err);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Residual add fused with the norms around it.  One block per row.
+//   b   = branch row                      (optional)
+//   b   = b * rsqrt(mean(b^2) + eps_post) * (w_post [+ 1])   (if w_post)
+//   h  += b                               (written back unless rows are gathered)
+//   y   = h * rsqrt(mean(h^2) + eps_pre) * (w_pre [+ 1])     (if w_pre), stored as T
+// With `rows`, block r works on row rows[r] and writes y[r]; h is left untouched.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict__ branch,
+                                     const void* __restrict__ w_post, int post_f32, float eps_post,
+                                     int post_plus_one, const void* __restrict__ w_pre, int pre_f32,
+                                     float eps_pre, int pre_plus_one, const int* __restrict__ rows,
+                                     T* __restrict__ y, int width, int num_rows_total, int* err) {
+  extern __shared__ float row[];  // width floats + 33 scratch
+  float* scratch = row + width;
+  const int r = blockIdx.x;
+  int src = rows ? rows[r] : r;
+  if (src < 0 || src >= num_rows_total) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_ROW);
+    src = 0;
+  }
+  float* hp = h + (size_t)src * width;
+  float rstd_b = 1.f;
+  if (branch) {
+    const T* bp = branch + (size_t)src * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float b = to_f32<T>(bp[i]);
+      row[i] = b;
+      ss += b * b;
+    }
+    if (w_post) {
+      ss = block_sum(ss, scratch);
+      rstd_b = 1.0f / sqrtf(ss / (float)width + eps_post);
+    }
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = hp[i];
+    if (branch) {
+      float b = row[i];
+      if (w_post) b = b * rstd_b * (load_scalar(w_post, post_f32, i) + (post_plus_one ? 1.f : 0.f));
+      v += b;
+      if (!rows) hp[i] = v;
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  if (w_pre) {
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)width + eps_pre);
+    T* yp = y + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      yp[i] = from_f32<T>(row[i] * rstd * (load_scalar(w_pre, pre_f32, i) + (pre_plus_one ? 1.f : 0.f)));
+  }
+}
+
+extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const void* w_post, int post_f32,
+                                float eps_post, int post_plus_one, const void* w_pre, int pre_f32,
+                                float eps_pre, int pre_plus_one, const int* rows, void* y, int num_rows,
+                                int width, int num_rows_total, int* err, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  const size_t smem = (size_t)(width + 33) * sizeof(float);
+  if (smem > 200 * 1024) return -2;  // refused: row does not fit shared memory
+  const int threads = width >= 2048 ? 512 : 256;
+  if (dtype == SB_DTYPE_F32) {
+    auto k = residual_norm_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<num_rows, threads, smem, stream>>>(h, (const float*)branch, w_post, post_f32, eps_post, post_plus_one,
+                                           w_pre, pre_f32, eps_pre, pre_plus_one, rows, (float*)y, width,
+                                           num_rows_total, err);
+  } else {
+    auto k = residual_norm_kernel<bf16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<num_rows, threads, smem, stream>>>(h, (const bf16*)branch, w_post, post_f32, eps_post, post_plus_one,
+                                           w_pre, pre_f32, eps_pre, pre_plus_one, rows, (bf16*)y, width,
+                                           num_rows_total, err);
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Stand-alone RMS norm of rows stored as Tin, result stored as Tout.
+// ---------------------------------------------------------------------------
+template <typename Tin, typename Tout>
+__global__ void rms_norm_kernel(const Tin* __restrict__ x, const void* __restrict__ w, int w_f32, float eps,
+                                int plus_one, Tout* __restrict__ y, int width) {
+  extern __shared__ float row[];
+  float* scratch = row + width;
+  const Tin* xp = x + (size_t)blockIdx.x * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = to_f32<Tin>(xp[i]);
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.0f / sqrtf(ss / (float)width + eps);
+  Tout* yp = y + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    yp[i] = from_f32<Tout>(row[i] * rstd * (load_scalar(w, w_f32, i) + (plus_one ? 1.f : 0.f)));
+}
+
+template <typename Tin, typename Tout>
+static int launch_rms_norm(const void* x, const void* w, int w_f32, float eps, int plus_one, void* y,
+                           int num_rows, int width, cudaStream_t stream) {
+  const size_t smem = (size_t)(width + 33) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  auto k = rms_norm_kernel<Tin, Tout>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  k<<<num_rows, 256, smem, stream>>>((const Tin*)x, w, w_f32, eps, plus_one, (Tout*)y, width);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int sb_rms_norm(const void* x, int in_dtype, const void* w, int w_f32, float eps, int plus_one,
+                           void* y, int out_dtype, int num_rows, int width, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  if (in_dtype == SB_DTYPE_F32 && out_dtype == SB_DTYPE_F32)
+    return launch_rms_norm<float, float>(x, w, w_f32, eps, plus_one, y, num_rows, width, stream);
+  if (in_dtype == SB_DTYPE_F32) return launch_rms_norm<float, bf16>(x, w, w_f32, eps, plus_one, y, num_rows, width, stream);
+  if (out_dtype == SB_DTYPE_F32) return launch_rms_norm<bf16, float>(x, w, w_f32, eps, plus_one, y, num_rows, width, stream);
+  return launch_rms_norm<bf16, bf16>(x, w, w_f32, eps, plus_one, y, num_rows, width, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Small helpers for norms the fused kernel does not know.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out,
+                                   int width, int num_rows_total, int* err) {
+  int src = rows[blockIdx.x];
+  if (src < 0 || src >= num_rows_total) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_ROW);
+    src = 0;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    out[(size_t)blockIdx.x * width + i] = x[(size_t)src * width + i];
+}
+
+extern "C" int sb_gather_rows(const void* x, int dtype, const int* rows, void* out, int num_rows, int width,
+                              int num_rows_total, int* err, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  if (dtype == SB_DTYPE_F32)
+    gather_rows_kernel<float><<<num_rows, 256, 0, stream>>>((const float*)x, rows, (float*)out, width, num_rows_total, err);
+  else
+    gather_rows_kernel<bf16><<<num_rows, 256, 0, stream>>>((const bf16*)x, rows, (bf16*)out, width, num_rows_total, err);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <typename T>
+__global__ void add_to_residual_kernel(float* __restrict__ h, const T* __restrict__ x, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) h[i] += to_f32<T>(x[i]);
+}
+
+extern "C" int sb_add_to_residual(float* h, const void* x, int dtype, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == SB_DTYPE_F32)
+    add_to_residual_kernel<float><<<blocks, 256, 0, stream>>>(h, (const float*)x, (size_t)n);
+  else
+    add_to_residual_kernel<bf16><<<blocks, 256, 0, stream>>>(h, (const bf16*)x, (size_t)n);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <typename Tin, typename Tout>
+__global__ void cast_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = from_f32<Tout>(to_f32<Tin>(x[i]));
+}
+
+extern "C" int sb_cast(const void* x, int in_dtype, void* y, int out_dtype, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (in_dtype == SB_DTYPE_F32 && out_dtype == SB_DTYPE_BF16)
+    cast_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)x, (bf16*)y, (size_t)n);
+  else if (in_dtype == SB_DTYPE_BF16 && out_dtype == SB_DTYPE_F32)
+    cast_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)x, (float*)y, (size_t)n);
+  else
+    return -3;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Rotation tables for the step's tokens: angle = position / timescale / scale_factor,
+// all float32, as the reference computes it; cos and sin are [T, half].
+// ---------------------------------------------------------------------------
+__global__ void rotation_tables_kernel(const int* __restrict__ positions, const float* __restrict__ timescale,
+                                       float scale_factor, float* __restrict__ cos_out,
+                                       float* __restrict__ sin_out, int num_tokens, int half) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= num_tokens * half) return;
+  const int t = i / half, j = i - t * half;
+  const float angle = (float)positions[t] / timescale[j] / scale_factor;
+  float s, c;
+  sincosf(angle, &s, &c);
+  cos_out[i] = c;
+  sin_out[i] = s;
+}
+
+extern "C" int sb_rotation_tables(const int* positions, const float* timescale, float scale_factor,
+                                  float* cos_out, float* sin_out, int num_tokens, int half,
+                                  cudaStream_t stream) {
+  const int n = num_tokens * half;
+  if (n == 0) return 0;
+  rotation_tables_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, timescale, scale_factor, cos_out,
+                                                              sin_out, num_tokens, half);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// From the fused projection qkv [T, (Hq + 2 Hkv) * dh]:
+//   q_out[t, n, :] = rotate(q) * q_scale
+//   cache[page, 0, m, offset, :] = rotate(k);  cache[page, 1, m, offset, :] = v
+// with page = block_table[seq(t), pos / page_size], offset = pos % page_size.
+// The halves of a head rotate together: (a, b) -> (a cos - b sin, b cos + a sin).
+// cos/sin may be null (no rotation).  Hkv_proj = 0: the projection holds q only.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, float q_scale, T* __restrict__ q_out,
+                                        T* __restrict__ cache, const int* __restrict__ block_table,
+                                        int max_pages, const int* __restrict__ token_seq,
+                                        const int* __restrict__ positions, int num_q_heads, int num_kv_proj,
+                                        int head_dim, int page_size, int num_pages, int write_cache, int* err) {
+  const int t = blockIdx.x;
+  const int half = head_dim / 2;
+  const int heads = num_q_heads + 2 * num_kv_proj;
+  const T* in = qkv + (size_t)t * heads * head_dim;
+  const int pos = positions[t];
+  long long page = -1;
+  int offset = 0;
+  if (write_cache && num_kv_proj > 0) {
+    page = block_table[(size_t)token_seq[t] * max_pages + pos / page_size];
+    offset = pos % page_size;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_PAGE);
+      page = -1;
+    }
+  }
+  for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+    const int hh = i / half, j = i - hh * half;
+    float a = to_f32<T>(in[hh * head_dim + j]);
+    float b = to_f32<T>(in[hh * head_dim + half + j]);
+    if (hh < num_q_heads + num_kv_proj && cos_t) {
+      const float c = cos_t[(size_t)t * half + j], s = sin_t[(size_t)t * half + j];
+      const float ra = a * c - b * s, rb = b * c + a * s;
+      a = ra;
+      b = rb;
+    }
+    if (hh < num_q_heads) {
+      T* o = q_out + ((size_t)t * num_q_heads + hh) * head_dim;
+      o[j] = from_f32<T>(a * q_scale);
+      o[half + j] = from_f32<T>(b * q_scale);
+    } else if (page >= 0) {
+      const int kv = hh < num_q_heads + num_kv_proj ? 0 : 1;
+      const int m = hh - num_q_heads - kv * num_kv_proj;
+      T* o = cache + ((((size_t)page * 2 + kv) * num_kv_proj + m) * page_size + offset) * head_dim;
+      o[j] = from_f32<T>(a);
+      o[half + j] = from_f32<T>(b);
+    }
+  }
+}
+
+extern "C" int sb_rope_cache_write(const void* qkv, int dtype, const float* cos_t, const float* sin_t,
+                                   float q_scale, void* q_out, void* cache, const int* block_table,
+                                   int max_pages, const int* token_seq, const int* positions, int num_tokens,
+                                   int num_q_heads, int num_kv_proj, int head_dim, int page_size,
+                                   int num_pages, int write_cache, int* err, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (head_dim % 2) return -4;
+  if (dtype == SB_DTYPE_F32)
+    rope_cache_write_kernel<float><<<num_tokens, 256, 0, stream>>>(
+        (const float*)qkv, cos_t, sin_t, q_scale, (float*)q_out, (float*)cache, block_table, max_pages,
+        token_seq, positions, num_q_heads, num_kv_proj, head_dim, page_size, num_pages, write_cache, err);
+  else
+    rope_cache_write_kernel<bf16><<<num_tokens, 256, 0, stream>>>(
+        (const bf16*)qkv, cos_t, sin_t, q_scale, (bf16*)q_out, (bf16*)cache, block_table, max_pages,
+        token_seq, positions, num_q_heads, num_kv_proj, head_dim, page_size, num_pages, write_cache, err);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Gated activation: z[t, f] = act(gate_up[t, f]) * gate_up[t, F + f].
+//   act 0: gelu, tanh form; 1: silu; 2: relu.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float apply_activation(float g, int act) {
+  if (act == 0) {
+    const float c = 0.7978845608028654f;  // sqrt(2 / pi)
+    return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+  }
+  if (act == 1) return g / (1.0f + expf(-g));
+  return fmaxf(g, 0.f);
+}
+
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden, int act,
+                                        size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / hidden, f = i - t * hidden;
+  const float g = to_f32<T>(gate_up[t * 2 * hidden + f]);
+  const float u = to_f32<T>(gate_up[t * 2 * hidden + hidden + f]);
+  z[i] = from_f32<T>(apply_activation(g, act) * u);
+}
+
+extern "C" int sb_gated_activation(const void* gate_up, int dtype, void* z, int num_tokens, int hidden, int act,
+                                   cudaStream_t stream) {
+  const size_t n = (size_t)num_tokens * hidden;
+  if (n == 0) return 0;
+  if (act < 0 || act > 2) return -5;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == SB_DTYPE_F32)
+    gated_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)z, hidden, act, n);
+  else
+    gated_activation_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)z, hidden, act, n);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap in place on float32 logits: x = cap * tanh(x / cap).  simply/model_lib.py:107-109.
+// ---------------------------------------------------------------------------
+__global__ void soft_cap_kernel(float* __restrict__ x, float cap, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int sb_soft_cap(float* x, float cap, long long n, cudaStream_t stream) {
+  if (n == 0 || cap <= 0.f) return 0;
+  soft_cap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, cap, (size_t)n);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

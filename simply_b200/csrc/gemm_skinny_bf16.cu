@@ -1,0 +1,180 @@
+// Weight-streaming matrix product for a handful of tokens (decode steps):
+//   out[M, N] = x[M, K] . w[N, K]^T,  bfloat16 in, float32 accumulate, M <= 32.
+//
+// With so few rows the product is bound by reading w once from HBM, so the kernel
+// is built around that stream.  The weight matrix is the 16-row operand of
+// mma.m16n8k16 and the tokens are the 8-column operand ("swapped"), both loaded
+// straight from global memory into registers with 16-byte loads.  The sum over K
+// does not care about order, so lane (g, t) of a warp takes the 8 consecutive k
+// values [32 s + 8 t, 32 s + 8 t + 8) of step s for weight rows g and g + 8 and
+// for token g, and feeds them to two mma's; no shared-memory staging or
+// transposition is needed.  A block owns 16 weight rows; its warps split K and
+// add their partial sums through shared memory in a fixed order.
+//
+// Epilogues: 0 store as bfloat16; 1 store float32 with an optional soft cap
+// (simply/model_lib.py:107-109, the output layer); 2 gated activation: the block
+// also owns rows [N/2 + n0, N/2 + n0 + 16) and stores act(gate) * up
+// (simply/model_lib.py:722-726).
+#include "common.cuh"
+
+__device__ __forceinline__ float skinny_activation(float g, int act) {
+  if (act == 0) {
+    const float c = 0.7978845608028654f;
+    return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+  }
+  if (act == 1) return g / (1.0f + expf(-g));
+  return fmaxf(g, 0.f);
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_stream16(const bf16* p) {
+  return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+
+// MT: token tiles of 8.  WARPS: warps per block (split of K).  EPI: epilogue.
+template <int MT, int WARPS, int EPI>
+__global__ void __launch_bounds__(WARPS * 32)
+skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void* __restrict__ out, int M,
+                   int N, int K, float cap, int act) {
+  constexpr int SETS = EPI == 2 ? 2 : 1;
+  __shared__ float partial[WARPS][SETS][MT][16][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_out = EPI == 2 ? N / 2 : N;  // rows a block set ranges over
+  const int n0 = blockIdx.x * 16;
+  // Rows past the end are clamped for loading and dropped when storing.
+  const bf16* wr[SETS][2];
+#pragma unroll
+  for (int s = 0; s < SETS; ++s) {
+    wr[s][0] = w + (size_t)(s * n_out + min(n0 + g, n_out - 1)) * K;
+    wr[s][1] = w + (size_t)(s * n_out + min(n0 + g + 8, n_out - 1)) * K;
+  }
+  const bf16* xr[MT];
+  bool xok[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    xok[mt] = mt * 8 + g < M;
+    xr[mt] = x + (size_t)min(mt * 8 + g, M - 1) * K;
+  }
+  float acc[SETS][MT][4];
+#pragma unroll
+  for (int s = 0; s < SETS; ++s)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[s][mt][i] = 0.f;
+
+  const int steps = (K + 31) / 32;
+  constexpr int UNROLL = SETS == 2 ? 2 : 4;
+  for (int s0 = warp; s0 < steps; s0 += WARPS * UNROLL) {
+    uint4 wa[UNROLL][SETS][2];
+    uint4 xv[UNROLL][MT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (s0 + u * WARPS) * 32 + t * 8;
+      const bool ok = k < K;  // K is a multiple of 8, so a chunk is whole or absent
+#pragma unroll
+      for (int s = 0; s < SETS; ++s) {
+        wa[u][s][0] = ok ? load_stream16(wr[s][0] + k) : make_uint4(0, 0, 0, 0);
+        wa[u][s][1] = ok ? load_stream16(wr[s][1] + k) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        xv[u][mt] = (ok && xok[mt]) ? __ldg(reinterpret_cast<const uint4*>(xr[mt] + k)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int s = 0; s < SETS; ++s)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16_16816(acc[s][mt], wa[u][s][0].x, wa[u][s][1].x, wa[u][s][0].y, wa[u][s][1].y, xv[u][mt].x,
+                         xv[u][mt].y);
+          mma_bf16_16816(acc[s][mt], wa[u][s][0].z, wa[u][s][1].z, wa[u][s][0].w, wa[u][s][1].w, xv[u][mt].z,
+                         xv[u][mt].w);
+        }
+  }
+  // acc[..][0,1]: weight row g, tokens 2t, 2t+1; acc[..][2,3]: weight row g + 8.
+#pragma unroll
+  for (int s = 0; s < SETS; ++s)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      partial[warp][s][mt][g][2 * t] = acc[s][mt][0];
+      partial[warp][s][mt][g][2 * t + 1] = acc[s][mt][1];
+      partial[warp][s][mt][g + 8][2 * t] = acc[s][mt][2];
+      partial[warp][s][mt][g + 8][2 * t + 1] = acc[s][mt][3];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < MT * 16 * 8; i += WARPS * 32) {
+    // Consecutive threads take consecutive weight rows: consecutive addresses of `out`.
+    const int row = i % 16, tok8 = (i / 16) % 8, mt = i / 128;
+    const int token = mt * 8 + tok8, n = n0 + row;
+    if (token >= M || n >= n_out) continue;
+    float v[SETS];
+#pragma unroll
+    for (int s = 0; s < SETS; ++s) {
+      float sum = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < WARPS; ++wi) sum += partial[wi][s][mt][row][tok8];
+      v[s] = sum;
+    }
+    const size_t o = (size_t)token * n_out + n;
+    if (EPI == 0) {
+      reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v[0]);
+    } else if (EPI == 1) {
+      reinterpret_cast<float*>(out)[o] = cap > 0.f ? cap * tanhf(v[0] / cap) : v[0];
+    } else {
+      // Round gate and up to bfloat16 first, as the unfused path stores them.
+      const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
+      const float up = __bfloat162float(__float2bfloat16_rn(v[SETS - 1]));
+      reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(skinny_activation(gate, act) * up);
+    }
+  }
+}
+
+template <int MT, int WARPS>
+static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, int K, int epilogue, float cap,
+                         int act, cudaStream_t stream) {
+  const int n_out = epilogue == 2 ? N / 2 : N;
+  const unsigned blocks = (unsigned)((n_out + 15) / 16);
+  if (epilogue == 0)
+    skinny_gemm_kernel<MT, WARPS, 0><<<blocks, WARPS * 32, 0, stream>>>(x, w, out, M, N, K, cap, act);
+  else if (epilogue == 1)
+    skinny_gemm_kernel<MT, WARPS, 1><<<blocks, WARPS * 32, 0, stream>>>(x, w, out, M, N, K, cap, act);
+  else
+    skinny_gemm_kernel<MT, WARPS, 2><<<blocks, WARPS * 32, 0, stream>>>(x, w, out, M, N, K, cap, act);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Returns -9 when the shape is outside what the kernel takes (the caller then
+// uses the library product): M > 32, K not a multiple of 8, N odd for the gated epilogue.
+extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, int epilogue,
+                                   float cap, int act, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M > 32 || K % 8 != 0 || K <= 0 || epilogue < 0 || epilogue > 2) return -9;
+  if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 2)) return -9;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)w;
+  const int n_out = epilogue == 2 ? N / 2 : N;
+  // Few blocks: more warps per block so that enough loads are in flight per SM.
+  const bool wide = (n_out + 15) / 16 < 4 * 148 && K >= 16 * 32 * 4;
+  if (M <= 8) {
+    return wide ? launch_skinny<1, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream)
+                : launch_skinny<1, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+  }
+  if (M <= 16) {
+    return wide ? launch_skinny<2, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream)
+                : launch_skinny<2, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+  }
+  // (8 warps only: with 16 the partial sums of the gated epilogue outgrow static shared memory.)
+  return launch_skinny<4, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+}

@@ -1,0 +1,302 @@
+"""The kernel table: every device operation the engine's parts call.
+
+`CudaOps(dtype)` is the only implementation in the package.  It needs a CUDA
+device and the compiled library and raises if either is missing; there is no
+CPU path.  `dtype` is the activation and cache dtype: `torch.bfloat16` is the
+serving path, `torch.float32` runs the whole model in true 32-bit arithmetic on
+CUDA cores (own SIMT matrix product, no tensor-core mode).
+
+Matrix products: in bfloat16, steps with at most 32 tokens use the engine's own
+weight-streaming kernel (with fused soft-cap or gated-activation epilogues);
+larger ones go to the library product (cuBLAS through torch.mm), as the
+reference leaves them to XLA.  Everything else (attention over the paged cache,
+norms, rotation, cache write, activation, embedding, sampling) is hand-written.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import numpy as np
+import torch
+
+from simply_b200.kernels import build
+
+_F32, _BF16 = 0, 1
+_ERRORS = {
+    1: "a block-table entry outside the page pool was about to be followed",
+    2: "a token id outside the embedding table",
+    4: "a gather row outside the batch",
+}
+_STATUS = {
+    -2: "row too wide for the norm kernel's shared-memory buffer",
+    -3: "unsupported cast",
+    -4: "head size must be even",
+    -5: "unknown activation code",
+    -6: "too many rows for one launch of the float32 product",
+    -7: "head size outside the attention kernel's range",
+    -8: "query heads are no multiple of key/value heads",
+    -9: "shape outside the weight-streaming product's range",
+}
+
+
+def _code(t: torch.Tensor) -> int:
+  if t.dtype == torch.float32:
+    return _F32
+  if t.dtype == torch.bfloat16:
+    return _BF16
+  raise TypeError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: torch.Tensor | None):
+  return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+class KernelError(RuntimeError):
+  pass
+
+
+class CudaOps:
+
+  name = "cuda"
+  # Largest token count the weight-streaming product takes.
+  skinny_max_rows = 16
+
+  def __init__(self, dtype: torch.dtype = torch.bfloat16, device: str | torch.device = "cuda"):
+    if dtype not in (torch.float32, torch.bfloat16):
+      raise TypeError(f"activation dtype must be float32 or bfloat16, got {dtype}")
+    if not torch.cuda.is_available():
+      raise KernelError("simply_b200 needs a CUDA device (sm_100a); there is no CPU path")
+    self.dtype = dtype
+    self.device = torch.device(device)
+    self.lib = build.load()
+    major, minor = torch.cuda.get_device_capability(self.device)
+    if major != 10:
+      raise KernelError(f"kernels are built for sm_100a; this device is sm_{major}{minor}")
+    self._declare()
+    self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+    # The true 32-bit path must not be routed through a reduced-precision matrix mode.
+    torch.backends.cuda.matmul.allow_tf32 = False
+    self.launches = 0
+
+  # ---- plumbing -------------------------------------------------------------
+  def _declare(self) -> None:
+    c_int, c_float, c_void, c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+    protos = {
+        "sb_embed": [c_void, c_int, c_void, c_float, c_void, c_int, c_int, c_int, c_void, c_void],
+        "sb_residual_norm": [c_void, c_void, c_int, c_void, c_int, c_float, c_int, c_void, c_int, c_float,
+                             c_int, c_void, c_void, c_int, c_int, c_int, c_void, c_void],
+        "sb_rms_norm": [c_void, c_int, c_void, c_int, c_float, c_int, c_void, c_int, c_int, c_int, c_void],
+        "sb_gather_rows": [c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_void, c_void],
+        "sb_add_to_residual": [c_void, c_void, c_int, c_ll, c_void],
+        "sb_cast": [c_void, c_int, c_void, c_int, c_ll, c_void],
+        "sb_rotation_tables": [c_void, c_void, c_float, c_void, c_void, c_int, c_int, c_void],
+        "sb_rope_cache_write": [c_void, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int, c_void,
+                                c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void],
+        "sb_gated_activation": [c_void, c_int, c_void, c_int, c_int, c_int, c_void],
+        "sb_soft_cap": [c_void, c_float, c_ll, c_void],
+        "sb_gemm_f32_nt": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_void],
+        "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void],
+        "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
+                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
+        "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void],
+    }
+    for name, argtypes in protos.items():
+      fn = getattr(self.lib, name)
+      fn.argtypes = argtypes
+      fn.restype = c_int
+
+  def _stream(self):
+    return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+  def _call(self, name: str, *args) -> int:
+    rc = getattr(self.lib, name)(*args, self._stream())
+    self.launches += 1
+    if rc != 0 and rc != -9:
+      why = _STATUS.get(rc, f"CUDA error {rc}" if rc > 0 else f"status {rc}")
+      raise KernelError(f"{name}: {why}")
+    return rc
+
+  def _new(self, *shape, dtype=None) -> torch.Tensor:
+    return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+  def check_errors(self) -> None:
+    """Reads the device error word (synchronises); raises if a kernel refused an access."""
+    word = int(self.err.item())
+    if word:
+      self.err.zero_()
+      reasons = [msg for bit, msg in _ERRORS.items() if word & bit]
+      raise KernelError("a kernel skipped an invalid access: " + "; ".join(reasons))
+
+  # ---- checks ---------------------------------------------------------------
+  def check_attention(self, head_dim: int, num_heads: int, num_kv_heads: int) -> None:
+    if head_dim <= 0 or head_dim % 2 or head_dim > 512:
+      raise KernelError(f"attention kernels take even head sizes up to 512, got {head_dim}")
+    if num_heads % num_kv_heads:
+      raise KernelError(f"{num_heads} query heads are no multiple of {num_kv_heads} key/value heads")
+
+  # ---- dense ----------------------------------------------------------------
+  def embed(self, table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+    if table.dtype == torch.bfloat16:
+      # The reference rounds the constant to the activation dtype (simply/utils/module.py:477-481).
+      scale = float(torch.tensor(scale, dtype=torch.float32).to(torch.bfloat16))
+    out = self._new(ids.numel(), table.shape[1], dtype=torch.float32)
+    self._call("sb_embed", _ptr(table), _code(table), _ptr(ids), float(scale), _ptr(out), ids.numel(),
+               table.shape[1], table.shape[0], _ptr(self.err))
+    return out
+
+  def cast(self, x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+      return x
+    out = self._new(*x.shape, dtype=dtype)
+    self._call("sb_cast", _ptr(x), _code(x), _ptr(out), _code(out), x.numel())
+    return out
+
+  def linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [M, K] . w[N, K]^T -> [M, N] in the activation dtype."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.dtype == torch.float32:
+      # Float32 weights (the 32-bit path, or a tensor stored in 32 bits): true float32 product.
+      xf = self.cast(x, torch.float32)
+      out = self._new(m, n, dtype=torch.float32)
+      self._call("sb_gemm_f32_nt", _ptr(xf), _ptr(w), _ptr(out), m, n, k, 0.0)
+      return self.cast(out, self.dtype)
+    x = self.cast(x, torch.bfloat16)
+    if m <= self.skinny_max_rows:
+      out = self._new(m, n, dtype=torch.bfloat16)
+      if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w), _ptr(out), m, n, k, 0, 0.0, 0) == 0:
+        return out
+    return torch.mm(x, w.t())
+
+  def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, activation: int) -> torch.Tensor:
+    """act(x . w_gate^T) * (x . w_up^T) with w_gate_up = [gate rows; up rows]: [M, N/2]."""
+    m, k = x.shape
+    n = w_gate_up.shape[0]
+    if w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m <= self.skinny_max_rows:
+      out = self._new(m, n // 2, dtype=torch.bfloat16)
+      if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n, k, 2, 0.0,
+                    activation) == 0:
+        return out
+    return self.gated_activation(self.linear(x, w_gate_up), activation)
+
+  def lm_head(self, x: torch.Tensor, table: torch.Tensor, cap: float) -> torch.Tensor:
+    """float32 logits [R, vocab] = softcap(x . table^T)."""
+    r, k = x.shape
+    v = table.shape[0]
+    out = self._new(r, v, dtype=torch.float32)
+    if table.dtype == torch.float32:
+      xf = self.cast(x, torch.float32)
+      self._call("sb_gemm_f32_nt", _ptr(xf), _ptr(table), _ptr(out), r, v, k, float(cap))
+      return out
+    x = self.cast(x, torch.bfloat16)
+    chunk = 32
+    if r > chunk and k % 8 == 0:
+      try:
+        torch.mm(x, table.t(), out_dtype=torch.float32, out=out)
+        self._call("sb_soft_cap", _ptr(out), float(cap), out.numel())
+        return out
+      except (TypeError, RuntimeError):
+        pass
+    if k % 8:
+      raise KernelError(f"the output layer's width {k} must be a multiple of 8 in bfloat16")
+    for r0 in range(0, r, chunk):
+      rows = min(chunk, r - r0)
+      self._call("sb_gemm_skinny_bf16", _ptr(x[r0:]), _ptr(table), _ptr(out[r0:]), rows, v, k, 1,
+                 float(cap), 0)
+    return out
+
+  def gated_activation(self, gate_up: torch.Tensor, activation: int) -> torch.Tensor:
+    t, two_f = gate_up.shape
+    out = self._new(t, two_f // 2, dtype=gate_up.dtype)
+    self._call("sb_gated_activation", _ptr(gate_up), _code(gate_up), _ptr(out), t, two_f // 2, activation)
+    return out
+
+  # ---- norms ----------------------------------------------------------------
+  def rms_norm(self, x: torch.Tensor, w: torch.Tensor, eps: float, plus_one: bool) -> torch.Tensor:
+    out = self._new(*x.shape)
+    self._call("sb_rms_norm", _ptr(x), _code(x), _ptr(w), int(w.dtype == torch.float32), float(eps),
+               int(plus_one), _ptr(out), _code(out), x.shape[0], x.shape[1])
+    return out
+
+  def residual_norm(self, h: torch.Tensor, branch: torch.Tensor | None, post: Any, pre: Any,
+                    rows: torch.Tensor | None) -> torch.Tensor | None:
+    """h += norm_post(branch); returns norm_pre(h) in the activation dtype (see csrc/elementwise.cu)."""
+    width = h.shape[1]
+    num_rows = h.shape[0] if rows is None else rows.numel()
+    y = self._new(num_rows, width) if pre is not None else None
+    if branch is None and pre is None:
+      return None
+    if branch is not None and branch.dtype != self.dtype:
+      branch = self.cast(branch, self.dtype)
+    wp, wq = (post.weight if post is not None else None), (pre.weight if pre is not None else None)
+    self._call(
+        "sb_residual_norm", _ptr(h), _ptr(branch), _BF16 if self.dtype == torch.bfloat16 else _F32,
+        _ptr(wp), int(wp is not None and wp.dtype == torch.float32),
+        float(post.eps) if post is not None else 0.0, int(post.plus_one) if post is not None else 0,
+        _ptr(wq), int(wq is not None and wq.dtype == torch.float32),
+        float(pre.eps) if pre is not None else 0.0, int(pre.plus_one) if pre is not None else 0,
+        _ptr(rows), _ptr(y), num_rows, width, h.shape[0], _ptr(self.err))
+    return y
+
+  def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    out = self._new(rows.numel(), x.shape[1], dtype=x.dtype)
+    self._call("sb_gather_rows", _ptr(x), _code(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1],
+               x.shape[0], _ptr(self.err))
+    return out
+
+  def add_to_residual(self, h: torch.Tensor, x: torch.Tensor) -> None:
+    self._call("sb_add_to_residual", _ptr(h), _ptr(x), _code(x), h.numel())
+
+  # ---- positions ------------------------------------------------------------
+  def rotation_tables(self, positions: torch.Tensor, timescale: torch.Tensor, scale_factor: float):
+    t, half = positions.numel(), timescale.numel()
+    cos = self._new(t, half, dtype=torch.float32)
+    sin = self._new(t, half, dtype=torch.float32)
+    self._call("sb_rotation_tables", _ptr(positions), _ptr(timescale), float(scale_factor), _ptr(cos),
+               _ptr(sin), t, half)
+    return cos, sin
+
+  def rope_and_cache_write(self, qkv: torch.Tensor, tables, q_scale: float, num_heads: int,
+                           num_kv_heads: int, head_dim: int, storage: torch.Tensor | None,
+                           block_table: torch.Tensor, ctx: Any) -> torch.Tensor:
+    t = qkv.shape[0]
+    q = self._new(t, num_heads, head_dim, dtype=qkv.dtype)
+    cos, sin = tables if tables is not None else (None, None)
+    if storage is not None and storage.dtype != qkv.dtype:
+      raise KernelError("cache and activations must share one dtype")
+    self._call("sb_rope_cache_write", _ptr(qkv), _code(qkv), _ptr(cos), _ptr(sin), float(q_scale), _ptr(q),
+               _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
+               _ptr(ctx.positions), t, num_heads, num_kv_heads, head_dim, ctx.page_size,
+               storage.shape[0] if storage is not None else 0, int(storage is not None), _ptr(self.err))
+    return q
+
+  # ---- attention ------------------------------------------------------------
+  def paged_attention(self, q: torch.Tensor, storage: torch.Tensor, block_table: torch.Tensor, ctx: Any, *,
+                      num_heads: int, num_kv_heads: int, head_dim: int, logit_softcap: float,
+                      window: int | None) -> torch.Tensor:
+    t = q.shape[0]
+    out = self._new(t, num_heads * head_dim, dtype=q.dtype)
+    self._call("sb_paged_attention_generic", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
+               block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
+               num_kv_heads, head_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
+               int(window or 0), _ptr(self.err))
+    return out
+
+  # ---- sampling -------------------------------------------------------------
+  def sample(self, logits: torch.Tensor, temperature, top_k, top_p, seed, position) -> torch.Tensor:
+    """One token per row of float32 logits; the other arguments are host sequences."""
+    r, vocab = logits.shape
+    params = np.zeros((r, 6), dtype=np.int32)
+    params[:, 0] = np.asarray(temperature, dtype=np.float32).view(np.int32)
+    params[:, 1] = np.asarray(top_k, dtype=np.int32)
+    params[:, 2] = np.asarray(top_p, dtype=np.float32).view(np.int32)
+    seeds = np.asarray([int(s) & 0xFFFFFFFFFFFFFFFF for s in seed], dtype=np.uint64)
+    params[:, 3] = (seeds & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)
+    params[:, 4] = (seeds >> np.uint64(32)).astype(np.uint32).view(np.int32)
+    params[:, 5] = np.asarray(position, dtype=np.int32)
+    dev_params = torch.from_numpy(params).to(self.device, non_blocking=True)
+    out = self._new(r, dtype=torch.int32)
+    self._call("sb_sample", _ptr(logits.contiguous()), _ptr(dev_params), _ptr(out), r, vocab)
+    return out

@@ -46,6 +46,5 @@ class GatedFeedForward(FeedForward):
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
     ops = ctx.ops
-    gate_up = ops.linear(x, self.gate_up_weight)
-    z = ops.gated_activation(gate_up, self.activation)
+    z = ops.gated_linear(x, self.gate_up_weight, self.activation)
     return self.down_proj(z, ctx)

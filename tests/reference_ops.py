@@ -34,6 +34,15 @@ class ReferenceOps:
   def linear(self, x, w):
     return (x.float() @ w.float().t()).to(self.dtype)
 
+  def gated_linear(self, x, w_gate_up, activation):
+    return self.gated_activation(self.linear(x, w_gate_up), activation)
+
+  def cast(self, x, dtype):
+    return x.to(dtype)
+
+  def check_errors(self):
+    pass
+
   def embed(self, table, ids, scale):
     s = torch.tensor(scale, dtype=torch.float32)
     if table.dtype == torch.bfloat16:

@@ -1,0 +1,329 @@
+"""Each CUDA kernel alone against its plain PyTorch statement (tests/reference_ops.py),
+at sizes other than the tiny models': widths and vocabularies that are no power of
+two, head sizes in steps of 16, odd head counts and groups, several page sizes."""
+
+import math
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from tests.kernel_util import make_scenario
+from tests.plain import gemma2_plain as plain
+from tests.reference_ops import ReferenceOps
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+@pytest.fixture(scope="module")
+def table():
+  from simply_b200.kernels.ops import CudaOps
+  return {dt: CudaOps(dt) for dt in DTYPES}
+
+
+def tol(dtype, scale=1.0):
+  # float32: sums in a different order; bfloat16: one rounding of the result (2^-9 relative)
+  # on top of float32 arithmetic inside.
+  return dict(atol=2e-5 * scale, rtol=2e-5) if dtype == torch.float32 else dict(atol=1e-2 * scale, rtol=1e-2)
+
+
+def close(got, want, dtype, scale=1.0):
+  torch.testing.assert_close(got.float().cpu(), want.float().cpu(), **tol(dtype, scale))
+
+
+def norm_part(width, dtype, plus_one=True, eps=1e-6, seed=0, device="cuda"):
+  g = torch.Generator().manual_seed(seed)
+  w = (torch.randn(width, generator=g) * 0.3).to(dtype).to(device)
+  return types.SimpleNamespace(weight=w, eps=eps, plus_one=plus_one)
+
+
+# ---- embedding ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_embed(table, dtype):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  vocab, width = 1003, 72
+  t = torch.randn(vocab, width).to(dtype).cuda()
+  ids = torch.randint(0, vocab, (37,), dtype=torch.int32).cuda()
+  got = ops.embed(t, ids, math.sqrt(width))
+  assert got.dtype == torch.float32
+  torch.testing.assert_close(got.cpu(), ref.embed(t.cpu(), ids.cpu(), math.sqrt(width)), atol=1e-6, rtol=1e-6)
+  ops.check_errors()
+
+
+# ---- norms --------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("width", [72, 2304, 3000])
+@pytest.mark.parametrize("variant", ["pre_only", "post_pre", "add_only", "post_only", "rows"])
+def test_residual_norm(table, dtype, width, variant):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  rows_total = 19
+  h = torch.randn(rows_total, width) * 3
+  branch = (torch.randn(rows_total, width) * 2).to(dtype)
+  post = norm_part(width, dtype, True, 1e-6, 1)
+  pre = norm_part(width, torch.float32 if variant == "post_pre" else dtype, variant != "post_only", 1e-5, 2)
+  rows = None
+  if variant == "pre_only":
+    args = (None, None, pre)
+  elif variant == "post_pre":
+    args = (branch, post, pre)
+  elif variant == "add_only":
+    args = (branch, None, pre)
+  elif variant == "post_only":
+    args = (branch, post, None)
+  else:
+    args = (branch, post, pre)
+    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32)
+
+  def cpu(p):
+    return None if p is None else types.SimpleNamespace(weight=p.weight.cpu(), eps=p.eps, plus_one=p.plus_one)
+
+  h_ref = h.clone()
+  want = ref.residual_norm(h_ref, None if args[0] is None else args[0].clone(), cpu(args[1]), cpu(args[2]), rows)
+  h_dev = h.cuda()
+  got = ops.residual_norm(h_dev, None if args[0] is None else args[0].cuda(), args[1], args[2],
+                          None if rows is None else rows.cuda())
+  if want is None:
+    assert got is None
+  else:
+    close(got, want, dtype, scale=3.0)
+  if rows is None:
+    torch.testing.assert_close(h_dev.cpu(), h_ref, atol=1e-5, rtol=1e-5)
+  else:
+    torch.testing.assert_close(h_dev.cpu(), h)  # untouched when rows are gathered
+  ops.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_rms_norm_and_helpers(table, dtype):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  x = torch.randn(11, 200)
+  n = norm_part(200, dtype, False, 1e-5)
+  for xin in (x, x.to(dtype)):
+    close(ops.rms_norm(xin.cuda(), n.weight, n.eps, n.plus_one), ref.rms_norm(xin, n.weight.cpu(), n.eps, n.plus_one), dtype, 3.0)
+  rows = torch.tensor([3, 3, 10, 0], dtype=torch.int32)
+  assert torch.equal(ops.gather_rows(x.cuda(), rows.cuda()).cpu(), x[rows.long()])
+  h = x.clone().cuda()
+  ops.add_to_residual(h, x.to(dtype).cuda())
+  torch.testing.assert_close(h.cpu(), x + x.to(dtype).float())
+
+
+# ---- rotation and cache write ----------------------------------------------------
+@pytest.mark.parametrize("theta,half", [(10000.0, 8), (500000.0, 24), (10000.0, 128)])
+def test_rotation_tables(table, theta, half):
+  ops, ref = table[torch.float32], ReferenceOps(torch.float32)
+  pos = torch.tensor([0, 1, 2, 63, 64, 1000, 8191, 40000], dtype=torch.int32)
+  frac = (2 * np.arange(half) / (2 * half)).astype(np.float32)
+  ts = torch.from_numpy(np.power(np.float32(theta), frac).astype(np.float32))
+  cos, sin = ops.rotation_tables(pos.cuda(), ts.cuda(), 1.0)
+  rc, rs = ref.rotation_tables(pos, ts, 1.0)
+  # Same float32 angle on both sides; sin/cos implementations differ by a few ulp.
+  torch.testing.assert_close(cos.cpu(), rc, atol=2e-6, rtol=0)
+  torch.testing.assert_close(sin.cpu(), rs, atol=2e-6, rtol=0)
+  # Against float64 angles the float32 angle itself is off by up to pos * 2^-24.
+  exact = pos.double()[:, None] / ts.double()[None, :]
+  assert (cos.cpu().double() - torch.cos(exact)).abs().max() < 40000 * 2.0 ** -23
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("hq,hkv,dh,ps", [(4, 1, 16, 4), (6, 2, 48, 8), (3, 3, 256, 64), (8, 4, 112, 16)])
+def test_rope_and_cache_write(table, dtype, hq, hkv, dh, ps):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  seqs = [(0, 9), (37, 1), (130, 21), (5, 2)]
+  sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=None, page_size=ps, dtype=dtype,
+                     device="cuda", ops=ops, seed=3)
+  t = sc.ctx.num_tokens
+  qkv = torch.randn(t, (hq + 2 * hkv) * dh).to(dtype).cuda()
+  rot = ops.rotation_tables(sc.ctx.positions, torch.linspace(1, 900, dh // 2).cuda(), 1.0)
+  st_ref = sc.storage.clone()
+  q_ref = ref.rope_and_cache_write(qkv, rot, 0.37, hq, hkv, dh, st_ref, sc.block_table, sc.ctx)
+  q = ops.rope_and_cache_write(qkv, rot, 0.37, hq, hkv, dh, sc.storage, sc.block_table, sc.ctx)
+  ops.check_errors()
+  close(q, q_ref, dtype, 3.0)
+  # Written places agree; every other place of the cache is untouched (NaN stays NaN, values stay).
+  torch.testing.assert_close(sc.storage.float().cpu(), st_ref.float().cpu(), equal_nan=True, **tol(dtype, 3.0))
+  # No rotation, and a projection that holds q only (a layer that reads another layer's cache).
+  q_only = torch.randn(t, hq * dh).to(dtype).cuda()
+  close(ops.rope_and_cache_write(q_only, None, 1.0, hq, 0, dh, None, sc.block_table, sc.ctx).reshape(t, -1),
+        q_only, dtype)
+
+
+# ---- feed-forward pieces ---------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_gated_activation(table, dtype, act):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  gu = (torch.randn(13, 2 * 330) * 3).to(dtype)
+  close(ops.gated_activation(gu.cuda(), act), ref.gated_activation(gu, act), dtype, 3.0)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (5, 200, 72), (17, 1000, 96), (70, 130, 33), (130, 65, 300)])
+def test_linear_float32_is_true_float32(table, m, n, k):
+  ops = table[torch.float32]
+  x, w = torch.randn(m, k), torch.randn(n, k)
+  got = ops.linear(x.cuda(), w.cuda()).cpu()
+  want = (x.double() @ w.double().t())
+  # A reduced-precision matrix mode (TF32: 10-bit mantissa) would miss this by 100x.
+  assert (got.double() - want).abs().max() < 1e-6 * k ** 0.5 * 8
+  # The sum over K does not depend on what else is in the batch.
+  alone = ops.linear(x[m // 2:m // 2 + 1].cuda(), w.cuda()).cpu()
+  assert torch.equal(alone[0], got[m // 2])
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 200])
+@pytest.mark.parametrize("n,k", [(48, 64), (1000, 96), (2304, 2048), (100, 328)])
+def test_linear_bfloat16(table, m, n, k):
+  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
+  x = torch.randn(m, k).to(torch.bfloat16)
+  w = (torch.randn(n, k) / k ** 0.5).to(torch.bfloat16)
+  close(ops.linear(x.cuda(), w.cuda()), ref.linear(x, w), torch.bfloat16)
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 40])
+@pytest.mark.parametrize("f,k,act", [(160, 96, 0), (1000, 64, 1), (9216 // 4, 2304, 0)])
+def test_gated_linear(table, m, f, k, act):
+  for dtype in DTYPES:
+    ops, ref = table[dtype], ReferenceOps(dtype)
+    x = torch.randn(m, k).to(dtype)
+    w = (torch.randn(2 * f, k) / k ** 0.5 * 2).to(dtype)
+    close(ops.gated_linear(x.cuda(), w.cuda(), act), ref.gated_linear(x, w, act), dtype, 2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("r,v,k,cap", [(1, 1000, 96, 10.0), (7, 256, 64, 30.0), (45, 1003, 72, 0.0), (3, 25600, 2304, 30.0)])
+def test_lm_head(table, dtype, r, v, k, cap):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  x = (torch.randn(r, k) * 2).to(dtype)
+  t = torch.randn(v, k).to(dtype)
+  got = ops.lm_head(x.cuda(), t.cuda(), cap)
+  assert got.dtype == torch.float32
+  # The product is accumulated and capped in float32 in both dtypes.
+  torch.testing.assert_close(got.cpu(), ref.lm_head(x, t, cap), atol=2e-4 * k ** 0.5, rtol=1e-4)
+
+
+def test_weight_stored_in_32_bits_is_used_in_32_bits(table):
+  ops = table[torch.bfloat16]
+  x = torch.randn(4, 64).to(torch.bfloat16)
+  w = torch.randn(32, 64)  # float32 although the engine runs in bfloat16
+  got = ops.linear(x.cuda(), w.cuda())
+  assert got.dtype == torch.bfloat16
+  want = (x.float() @ w.t()).to(torch.bfloat16)
+  assert torch.equal(got.cpu(), want) or (got.cpu().float() - want.float()).abs().max() <= 2 ** -7 * want.abs().max()
+
+
+# ---- attention ---------------------------------------------------------------------
+ATTN_CASES = [
+    # hq, hkv, dh, page, window, cap
+    (4, 1, 16, 4, 8, 50.0),
+    (6, 2, 32, 8, 16, 20.0),
+    (8, 4, 256, 64, None, 50.0),
+    (8, 4, 256, 16, 100, 50.0),
+    (3, 3, 48, 16, None, 0.0),
+    (5, 1, 80, 32, 33, 30.0),
+    (32, 16, 128, 64, 70, 50.0),
+]
+SEQS = [(0, 19), (250, 1), (64, 64), (3, 2), (129, 37), (511, 1)]
+
+
+def run_attention(ops, q, sc, hq, hkv, dh, cap, window):
+  return ops.paged_attention(q, sc.storage, sc.block_table, sc.ctx, num_heads=hq, num_kv_heads=hkv,
+                             head_dim=dh, logit_softcap=cap, window=window)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("hq,hkv,dh,ps,window,cap", ATTN_CASES)
+def test_paged_attention_random(table, dtype, hq, hkv, dh, ps, window, cap):
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  sc = make_scenario(SEQS, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=dtype,
+                     device="cuda", ops=ops, seed=5)
+  q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 1.5).to(dtype).cuda()
+  got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+  ops.check_errors()
+  assert torch.isfinite(got).all(), "a page the request does not hold was read"
+  want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)
+  close(got, want, dtype, 2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("ps", [16, 64])
+@pytest.mark.parametrize("window", [None, 96])
+def test_paged_attention_one_key_stands_out(table, dtype, ps, window):
+  """One key matches the query far better than the rest and carries a value of its own.
+  Placed far back, at a page's edge and at the window's edge, it shows whether exactly
+  the right keys are visible."""
+  ops = table[dtype]
+  hq, hkv, dh, cap = 4, 2, 64, 50.0
+  hist = 700
+  sc = make_scenario([(hist, 1), (hist, 3)], num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps,
+                     dtype=dtype, device="cuda", ops=ops, seed=9)
+  g = sc.manager.groups[0]
+  direction = torch.nn.functional.normalize(torch.randn(dh), dim=0)
+  q = (direction * 9.0).expand(sc.ctx.num_tokens, hq, dh).contiguous().to(dtype).cuda()
+  w = window if window is not None else 10 ** 9
+  spots = [3, ps - 1, ps, hist - w, hist - w + 1, hist - w + 2, hist - 1, hist, hist + 1, hist + 2]
+  for spot in spots:
+    if spot < 0:
+      continue
+    backup = sc.storage.clone()
+    for slot, q_start, q_len in sc.seqs:
+      page = int(g.tables[slot, spot // ps])
+      if page < 0 or spot >= q_start + q_len:
+        continue  # given back (outside every window) or not yet there
+      sc.storage[page, 0, :, spot % ps, :] = (direction * 9.0).to(dtype).cuda()
+      sc.storage[page, 1, :, spot % ps, :] = 7.0
+    got = run_attention(ops, q, sc, hq, hkv, dh, cap, window).float().cpu().reshape(sc.ctx.num_tokens, hq, dh)
+    ops.check_errors()
+    row = 0
+    for slot, q_start, q_len in sc.seqs:
+      for i in range(q_len):
+        pos = q_start + i
+        visible = spot <= pos and (window is None or pos - spot < window)
+        mean = got[row].mean().item()
+        if visible:
+          assert mean > 6.5, (spot, pos, mean)  # e^(cap*tanh(81/50) - others) swamps ~700 ordinary keys
+        else:
+          assert abs(mean) < 1.0, (spot, pos, mean)
+        row += 1
+    sc.storage.copy_(backup)
+
+
+# ---- sampling ---------------------------------------------------------------------
+def test_sample_greedy_and_ties(table):
+  ops = table[torch.float32]
+  logits = torch.randn(5, 1003)
+  logits[2, 17] = logits[2, 900] = 9.0  # lowest index wins a tie
+  got = ops.sample(logits.cuda(), [0.0] * 5, [-1] * 5, [1.0] * 5, [0] * 5, [3] * 5).cpu()
+  want = torch.tensor([int(torch.argmax(r)) for r in logits])
+  want[2] = 17
+  assert torch.equal(got.long(), want)
+  got = ops.sample(logits.cuda(), [0.7] * 5, [1] * 5, [1.0] * 5, [0] * 5, [3] * 5).cpu()
+  assert torch.equal(got.long(), want)  # top_k == 1 is greedy
+
+
+@pytest.mark.parametrize("vocab", [256, 1003, 25601])
+def test_sample_matches_plain_statement(table, vocab):
+  ops = table[torch.float32]
+  rng = np.random.default_rng(vocab)
+  rows = 24
+  logits = torch.from_numpy(rng.normal(size=(rows, vocab)).astype(np.float32) * 3)
+  temperature = [0.8, 1.0, 0.3, 1.7] * (rows // 4)
+  top_k = [-1, 5, -1, 40, 7, -1] * (rows // 6)
+  top_p = [1.0, 1.0, 0.9, 0.5, 0.95, 0.2] * (rows // 6)
+  seed = [int(rng.integers(0, 2 ** 63)) for _ in range(rows)]
+  position = [int(rng.integers(1, 8192)) for _ in range(rows)]
+  got = ops.sample(logits.cuda(), temperature, top_k, top_p, seed, position).cpu().tolist()
+  want = [plain.sample_token(logits[i].numpy(), temperature[i], top_k[i], top_p[i], seed[i], position[i])
+          for i in range(rows)]
+  assert got == want
+
+
+def test_sample_is_distributed_as_softmax(table):
+  ops = table[torch.float32]
+  logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]]).repeat(4000, 1)
+  got = ops.sample(logits.cuda(), [1.0] * 4000, [-1] * 4000, [1.0] * 4000, list(range(4000)), [5] * 4000)
+  freq = torch.bincount(got.cpu().long(), minlength=5).float() / 4000
+  want = torch.softmax(logits[0], 0)
+  assert (freq - want).abs().max() < 0.03
