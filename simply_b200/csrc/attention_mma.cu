@@ -1,0 +1,519 @@
+// Ragged paged attention on tensor cores (bfloat16 in, float32 softmax and accumulate),
+// compiled once per head size (-DSB_HEAD_DIM=N, N a multiple of 16 up to 256).
+//
+//   s = q . k                 (q is already rotated and scaled)
+//   s = cap * tanh(s / cap)   if cap > 0          simply/model_lib.py:621-626
+//   keep k_pos <= q_pos and, with a window W, q_pos - k_pos < W
+//                                                 simply/model_lib.py:469-515
+//   p = softmax(s) in float32, o = p . v          simply/model_lib.py:633-637
+//   query head n reads kv head n / G              simply/model_lib.py:2306-2310
+//
+// Two kernels share the tile code.
+//  * prefill: a block owns 64 query rows of one (sequence, kv head): the G query heads
+//    of the group for 64 / G consecutive tokens, so a key/value tile that is brought
+//    to shared memory once serves the whole group.  Four warps own 16 rows each and
+//    walk the key tiles (64 keys) with an online softmax.
+//  * decode (at most 16 query rows per sequence and kv head, i.e. one or a few new
+//    tokens): the keys are cut into chunks at fixed absolute positions; a block owns
+//    one chunk, its four warps split every 64-key tile four ways, merge, and store a
+//    partial result (max, sum, normalised output) that `combine` merges over chunks in
+//    a fixed order.
+// Keys and values come from the paged cache through the block table with 16-byte
+// cp.async copies; rows outside what the request holds are zero-filled, never read.
+#include <float.h>
+
+#include "common.cuh"
+
+#ifndef SB_HEAD_DIM
+#define SB_HEAD_DIM 256
+#endif
+
+namespace {
+
+constexpr int DH = SB_HEAD_DIM;
+constexpr int PITCH = DH + 8;  // elements; the 16-byte pad spreads 8 consecutive rows over all banks
+constexpr int BN = 64;         // keys per tile
+constexpr int CPR = DH / 8;    // 16-byte chunks per row
+constexpr int NT = 128;        // threads per block
+constexpr float LOG2E = 1.4426950408889634f;
+
+static_assert(DH % 16 == 0 && DH >= 16 && DH <= 256, "head size must be a multiple of 16 up to 256");
+
+struct AttnParams {
+  const bf16* q;      // [T, Hq, DH]
+  const bf16* cache;  // [P, 2, Hkv, page, DH]
+  const int* block_table;
+  int max_pages;
+  const int* cu_q;     // [B + 1]
+  const int* q_start;  // [B]
+  bf16* out;           // [T, Hq * DH]
+  int num_q_heads, num_kv_heads, page_size, num_pages;
+  float cap;
+  int window;
+  const int* items;  // prefill: (sequence, first token of the tile); decode: (sequence, chunk)
+  int chunk;         // decode: keys per chunk (a multiple of BN)
+  float* part_o;     // decode: [items, Hkv, rows_max, DH]
+  float* part_ml;    // decode: [items, Hkv, rows_max, 2]
+  int rows_max;
+  int* err;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t r[4], const bf16* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t r[4], const bf16* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Brings keys [tile, tile + BN) of (sequence b, kv head m) to shared memory; positions
+// outside [kv_lo, kv_hi) and pages the request does not hold are zero-filled.
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, bf16* sk, bf16* sv, int tile, int kv_lo,
+                                             int kv_hi, int b, int m) {
+  const size_t head_stride = (size_t)p.page_size * DH;
+  const size_t v_offset = (size_t)p.num_kv_heads * head_stride;
+  for (int i = threadIdx.x; i < BN * CPR; i += NT) {
+    const int row = i / CPR, c = i - row * CPR;
+    const int j = tile + row;
+    bool valid = j >= kv_lo && j < kv_hi;
+    long long page = 0;
+    if (valid) {
+      page = p.block_table[(size_t)b * p.max_pages + j / p.page_size];
+      if (page < 0 || page >= p.num_pages) {
+        if (c == 0) atomicOr(p.err, SB_ERR_BAD_PAGE);
+        valid = false;
+        page = 0;
+      }
+    }
+    const bf16* src = p.cache + ((size_t)page * 2 * p.num_kv_heads + m) * head_stride +
+                      (size_t)(valid ? j % p.page_size : 0) * DH + c * 8;
+    cp_async16(sk + row * PITCH + c * 8, src, valid);
+    cp_async16(sv + row * PITCH + c * 8, src + v_offset, valid);
+  }
+}
+
+// Scores of one warp's 16 query rows against NKT * 8 keys that start at row `key0` of the tile.
+template <int NKT>
+__device__ __forceinline__ void scores(float (&s)[NKT][4], const bf16* sq_rows, const bf16* sk, int key0) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i < NKT; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < DH / 16; ++ks) {
+    uint32_t a[4];
+    ldmatrix_x4(a, sq_rows + (lane & 15) * PITCH + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int np = 0; np < NKT / 2; ++np) {
+      uint32_t r[4];
+      ldmatrix_x4(r, sk + (key0 + np * 16 + (lane >> 4) * 8 + (lane & 7)) * PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
+      mma16816(s[2 * np], a, r[0], r[1]);
+      mma16816(s[2 * np + 1], a, r[2], r[3]);
+    }
+  }
+}
+
+// Soft cap, mask, online softmax update and P.V for one warp.  `pos_a`, `pos_b`: positions of
+// the thread's two query rows (-1 for a padding row).  `j0`: position of the first of the
+// NKT * 8 keys.  m_* are kept in log2 units.
+template <int NKT>
+__device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8][4], float& m_a, float& m_b,
+                                           float& l_a, float& l_b, int pos_a, int pos_b, int j0, float cap,
+                                           int window, const bf16* sv, int key0) {
+  const int lane = threadIdx.x & 31, t = lane & 3;
+  const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+  float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NKT; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = j0 + i * 8 + 2 * t + (e & 1);
+      const int pos = e < 2 ? pos_a : pos_b;
+      float v = s[i][e];
+      if (cap > 0.f) v = cap * fast_tanh(v * inv_cap);
+      const bool keep = j <= pos && (window <= 0 || pos - j < window);
+      v = keep ? v * LOG2E : -INFINITY;
+      s[i][e] = v;
+      if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+    }
+  mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+  mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+  mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+  mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+  const float new_a = fmaxf(m_a, mx_a), new_b = fmaxf(m_b, mx_b);
+  const float use_a = new_a == -INFINITY ? 0.f : new_a, use_b = new_b == -INFINITY ? 0.f : new_b;
+  const float alpha_a = fast_exp2(m_a - use_a), alpha_b = fast_exp2(m_b - use_b);
+  m_a = new_a;
+  m_b = new_b;
+  float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+  for (int i = 0; i < NKT; ++i) {
+    s[i][0] = fast_exp2(s[i][0] - use_a);
+    s[i][1] = fast_exp2(s[i][1] - use_a);
+    s[i][2] = fast_exp2(s[i][2] - use_b);
+    s[i][3] = fast_exp2(s[i][3] - use_b);
+    sum_a += s[i][0] + s[i][1];
+    sum_b += s[i][2] + s[i][3];
+  }
+  l_a = l_a * alpha_a + sum_a;  // per-thread share of the row sum; the quad is added up at the end
+  l_b = l_b * alpha_b + sum_b;
+#pragma unroll
+  for (int d = 0; d < DH / 8; ++d) {
+    o[d][0] *= alpha_a;
+    o[d][1] *= alpha_a;
+    o[d][2] *= alpha_b;
+    o[d][3] *= alpha_b;
+  }
+#pragma unroll
+  for (int kk = 0; kk < NKT / 2; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < DH / 16; ++dp) {
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, sv + (key0 + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PITCH + dp * 16 + (lane >> 4) * 8);
+      mma16816(o[2 * dp], a, r[0], r[1]);
+      mma16816(o[2 * dp + 1], a, r[2], r[3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Prefill: grid (items, kv heads), 128 threads.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [64][PITCH]
+  bf16* sk = sq + 64 * PITCH;                    // [2][BN][PITCH]
+  bf16* sv = sk + 2 * BN * PITCH;                // [2][BN][PITCH]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int b = p.items[2 * blockIdx.x], i0 = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
+  const int group = p.num_q_heads / p.num_kv_heads;
+  const int tokens_per_tile = 64 / group;
+  const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
+  const int ntok = min(tokens_per_tile, q_len - i0);
+  const int rows_valid = ntok * group;
+
+  for (int i = threadIdx.x; i < 64 * CPR; i += NT) {
+    const int row = i / CPR, c = i - row * CPR;
+    const bool valid = row < rows_valid;
+    const int tok = valid ? i0 + row / group : i0, h = m * group + (valid ? row % group : 0);
+    cp_async16(sq + row * PITCH + c * 8, p.q + ((size_t)(row0 + tok) * p.num_q_heads + h) * DH + c * 8, valid);
+  }
+  const int p0 = qs + i0, p1 = qs + i0 + ntok - 1;
+  const int kv_lo = p.window > 0 ? max(qs - p.window + 1, 0) : 0;  // lowest key the request still holds
+  const int lo = p.window > 0 ? max(p0 - p.window + 1, 0) : 0;     // lowest key this tile can see
+  const int kv_hi = p1 + 1;
+  const int tile0 = (lo / BN) * BN;
+  const int n_tiles = (kv_hi - tile0 + BN - 1) / BN;
+  load_kv_tile(p, sk, sv, tile0, kv_lo, kv_hi, b, m);
+  cp_async_commit();
+
+  const int ra = warp * 16 + g, rb = ra + 8;
+  const int pos_a = ra < rows_valid ? p0 + ra / group : -1;
+  const int pos_b = rb < rows_valid ? p0 + rb / group : -1;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  float o[DH / 8][4];
+#pragma unroll
+  for (int d = 0; d < DH / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_kv_tile(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, tile0 + (it + 1) * BN, kv_lo,
+                   kv_hi, b, m);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float s[BN / 8][4];
+    scores<BN / 8>(s, sq + warp * 16 * PITCH, sk + stage * BN * PITCH, 0);
+    softmax_pv<BN / 8>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, tile0 + it * BN, p.cap, p.window,
+                       sv + stage * BN * PITCH, 0);
+    __syncthreads();
+  }
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+  if (ra < rows_valid) {
+    bf16* op = p.out + ((size_t)(row0 + i0 + ra / group) * p.num_q_heads + m * group + ra % group) * DH;
+#pragma unroll
+    for (int d = 0; d < DH / 8; ++d)
+      *reinterpret_cast<uint32_t*>(op + d * 8 + 2 * t) = pack_bf16(o[d][0] * inv_a, o[d][1] * inv_a);
+  }
+  if (rb < rows_valid) {
+    bf16* op = p.out + ((size_t)(row0 + i0 + rb / group) * p.num_q_heads + m * group + rb % group) * DH;
+#pragma unroll
+    for (int d = 0; d < DH / 8; ++d)
+      *reinterpret_cast<uint32_t*>(op + d * 8 + 2 * t) = pack_bf16(o[d][2] * inv_b, o[d][3] * inv_b);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode: grid (items, kv heads), 128 threads; a block owns one chunk of keys.
+// ---------------------------------------------------------------------------------------
+template <int STAGES>
+__global__ void __launch_bounds__(NT) attn_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [16][PITCH]
+  bf16* sk = sq + 16 * PITCH;                    // [STAGES][BN][PITCH]
+  bf16* sv = sk + STAGES * BN * PITCH;           // [STAGES][BN][PITCH]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int b = p.items[2 * blockIdx.x], chunk_index = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
+  if (b < 0) return;  // filler item of a fixed-size launch
+  const int group = p.num_q_heads / p.num_kv_heads;
+  const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
+  const int rows_valid = q_len * group;  // <= 16 by the host's routing
+  const int kv_lo = p.window > 0 ? max(qs - p.window + 1, 0) : 0;
+  const int kv_hi = qs + q_len;
+  const int begin = max(chunk_index * p.chunk, (kv_lo / BN) * BN);
+  const int end = min((chunk_index + 1) * p.chunk, kv_hi);
+  const int n_tiles = end > begin ? (end - begin + BN - 1) / BN : 0;
+
+  for (int i = threadIdx.x; i < 16 * CPR; i += NT) {
+    const int row = i / CPR, c = i - row * CPR;
+    const bool valid = row < rows_valid;
+    const int tok = valid ? row / group : 0, h = m * group + (valid ? row % group : 0);
+    cp_async16(sq + row * PITCH + c * 8, p.q + ((size_t)(row0 + tok) * p.num_q_heads + h) * DH + c * 8, valid);
+  }
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < n_tiles)
+      load_kv_tile(p, sk + st * BN * PITCH, sv + st * BN * PITCH, begin + st * BN, kv_lo, end, b, m);
+    cp_async_commit();
+  }
+  const int pos_a = g < rows_valid ? qs + g / group : -1;
+  const int pos_b = g + 8 < rows_valid ? qs + (g + 8) / group : -1;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  float o[DH / 8][4];
+#pragma unroll
+  for (int d = 0; d < DH / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it % STAGES;
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();  // tile `it` has landed; everyone is done with tile it - 1
+    if (it + STAGES - 1 < n_tiles) {
+      const int st = (it + STAGES - 1) % STAGES;
+      load_kv_tile(p, sk + st * BN * PITCH, sv + st * BN * PITCH, begin + (it + STAGES - 1) * BN, kv_lo, end, b, m);
+    }
+    cp_async_commit();
+    float s[2][4];
+    scores<2>(s, sq, sk + stage * BN * PITCH, warp * 16);
+    softmax_pv<2>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, begin + it * BN + warp * 16, p.cap, p.window,
+                  sv + stage * BN * PITCH, warp * 16);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+  // Merge the four warps (each saw a quarter of every tile) through shared memory.
+  float* wm = reinterpret_cast<float*>(sk);  // [4][16] max, [4][16] sum, then [4][rows_valid][DH]
+  float* wl = wm + 64;
+  float* wo = wl + 64;
+  if (t == 0) {
+    wm[warp * 16 + g] = m_a;
+    wm[warp * 16 + g + 8] = m_b;
+    wl[warp * 16 + g] = l_a;
+    wl[warp * 16 + g + 8] = l_b;
+  }
+  if (g < rows_valid) {
+#pragma unroll
+    for (int d = 0; d < DH / 8; ++d) {
+      wo[((size_t)warp * rows_valid + g) * DH + d * 8 + 2 * t] = o[d][0];
+      wo[((size_t)warp * rows_valid + g) * DH + d * 8 + 2 * t + 1] = o[d][1];
+    }
+  }
+  if (g + 8 < rows_valid) {
+#pragma unroll
+    for (int d = 0; d < DH / 8; ++d) {
+      wo[((size_t)warp * rows_valid + g + 8) * DH + d * 8 + 2 * t] = o[d][2];
+      wo[((size_t)warp * rows_valid + g + 8) * DH + d * 8 + 2 * t + 1] = o[d][3];
+    }
+  }
+  __syncthreads();
+  const size_t pidx = (size_t)blockIdx.x * p.num_kv_heads + m;
+  for (int i = threadIdx.x; i < rows_valid * DH; i += NT) {
+    const int r = i / DH, d = i - r * DH;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wm[w * 16 + r]);
+    float num = 0.f, den = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float sc = fast_exp2(wm[w * 16 + r] - mx);
+        num += sc * wo[((size_t)w * rows_valid + r) * DH + d];
+        den += sc * wl[w * 16 + r];
+      }
+    }
+    p.part_o[(pidx * p.rows_max + r) * DH + d] = den > 0.f ? num / den : 0.f;
+    if (d == 0) {
+      p.part_ml[(pidx * p.rows_max + r) * 2] = mx;
+      p.part_ml[(pidx * p.rows_max + r) * 2 + 1] = den;
+    }
+  }
+}
+
+// Merges the chunks of every (token, query head): one warp each, chunks in ascending order.
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                    const int* __restrict__ split_start, const int* __restrict__ split_count,
+                                    bf16* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
+                                    int rows_max) {
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)num_tokens * num_q_heads) return;
+  const int tkn = (int)(item / num_q_heads), h = (int)(item % num_q_heads);
+  const int b = token_seq[tkn];
+  const int count = split_count[b];
+  if (count <= 0) return;  // this sequence went through the prefill kernel
+  const int group = num_q_heads / num_kv_heads, m = h / group;
+  const int r = (tkn - cu_q[b]) * group + h % group;
+  const int first = split_start[b];
+  float mx = -INFINITY;
+  for (int s = 0; s < count; ++s)
+    mx = fmaxf(mx, part_ml[(((size_t)(first + s) * num_kv_heads + m) * rows_max + r) * 2]);
+  float acc[DH / 32 + 1];
+#pragma unroll
+  for (int i = 0; i < DH / 32 + 1; ++i) acc[i] = 0.f;
+  float den = 0.f;
+  for (int s = 0; s < count; ++s) {
+    const size_t pidx = ((size_t)(first + s) * num_kv_heads + m) * rows_max + r;
+    const float ms = part_ml[pidx * 2], ls = part_ml[pidx * 2 + 1];
+    if (ls <= 0.f) continue;
+    const float w = ls * fast_exp2(ms - mx);
+    den += w;
+#pragma unroll
+    for (int i = 0; i < DH / 32 + 1; ++i) {
+      const int d = lane + 32 * i;
+      if (d < DH) acc[i] += w * part_o[pidx * DH + d];
+    }
+  }
+  const float inv = den > 0.f ? 1.0f / den : 0.f;
+  bf16* op = out + ((size_t)tkn * num_q_heads + h) * DH;
+#pragma unroll
+  for (int i = 0; i < DH / 32 + 1; ++i) {
+    const int d = lane + 32 * i;
+    if (d < DH) op[d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+constexpr int DECODE_STAGES = 3;
+constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BN) * PITCH * sizeof(bf16);
+constexpr size_t DECODE_SMEM_KV = (size_t)(16 + 2 * DECODE_STAGES * BN) * PITCH * sizeof(bf16);
+constexpr size_t DECODE_SMEM_MERGE = 16 * PITCH * sizeof(bf16) + (128 + 4 * 16 * DH) * sizeof(float);
+constexpr size_t DECODE_SMEM = DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE;
+
+}  // namespace
+
+#define SB_CONCAT2(a, b) a##b
+#define SB_CONCAT(a, b) SB_CONCAT2(a, b)
+#define SB_FN(name) SB_CONCAT(SB_CONCAT(name, _hd), SB_HEAD_DIM)
+
+// Ragged prefill attention.  items: [num_items, 2] (sequence, first token of a 64 / G token tile).
+extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                      const int* cu_q, const int* q_start, void* out, int num_q_heads,
+                                      int num_kv_heads, int page_size, int num_pages, float cap, int window,
+                                      const int* items, int num_items, int* err, cudaStream_t stream) {
+  if (num_items == 0) return 0;
+  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > 64) return -8;
+  AttnParams p{};
+  p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
+  p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
+  p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
+  p.window = window; p.items = items; p.err = err;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)PREFILL_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attn_prefill_kernel<<<dim3(num_items, num_kv_heads), NT, PREFILL_SMEM, stream>>>(p);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Split-key attention for sequences with at most 16 query rows per kv head, and the merge.
+// items: [num_items, 2] (sequence or -1, chunk index); chunk: keys per chunk, a multiple of 64;
+// part_o / part_ml: scratch of num_items * Hkv * rows_max * (DH | 2) floats;
+// split_start / split_count: per sequence, its range of items (count 0: not handled here).
+extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                     const int* cu_q, const int* q_start, const int* token_seq, void* out,
+                                     int num_tokens, int num_q_heads, int num_kv_heads, int page_size,
+                                     int num_pages, float cap, int window, const int* items, int num_items,
+                                     int chunk, float* part_o, float* part_ml, int rows_max,
+                                     const int* split_start, const int* split_count, int* err,
+                                     cudaStream_t stream) {
+  if (num_items == 0) return 0;
+  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || rows_max > 16 || chunk % BN) return -8;
+  AttnParams p{};
+  p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
+  p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
+  p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
+  p.window = window; p.items = items; p.chunk = chunk; p.part_o = part_o; p.part_ml = part_ml;
+  p.rows_max = rows_max; p.err = err;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DECODE_STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attn_decode_kernel<DECODE_STAGES><<<dim3(num_items, num_kv_heads), NT, DECODE_SMEM, stream>>>(p);
+  SB_LAUNCH_CHECK();
+  const long long rows = (long long)num_tokens * num_q_heads;
+  attn_combine_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(
+      part_o, part_ml, token_seq, cu_q, split_start, split_count, (bf16*)out, num_tokens, num_q_heads,
+      num_kv_heads, rows_max);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

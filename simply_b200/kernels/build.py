@@ -35,17 +35,23 @@ class KernelBuildError(RuntimeError):
   pass
 
 
+# Sources that are compiled once per head size (-DSB_HEAD_DIM=N) into libraries of their own.
+PER_HEAD_DIM = ("attention_mma.cu",)
+
+
 def sources() -> list[str]:
-  return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+  return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)
+                if f.endswith(".cu") and f not in PER_HEAD_DIM)
 
 
 def _headers() -> list[str]:
   return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
 
 
-def _digest() -> str:
+def _digest(srcs: list[str] | None = None, extra: str = "") -> str:
   h = hashlib.sha256()
-  for path in sources() + _headers():
+  h.update(extra.encode())
+  for path in (sources() if srcs is None else srcs) + _headers():
     h.update(os.path.basename(path).encode())
     with open(path, "rb") as f:
       h.update(f.read())
@@ -80,24 +86,39 @@ def _say(msg: str) -> None:
 
 
 def build(verbose: bool = True, force: bool = False) -> str:
-  """Compiles the library if it is missing or stale; returns its path."""
+  """Compiles the core library if it is missing or stale; returns its path."""
+  return _build(sources(), LIB_NAME, [], verbose, force)
+
+
+def attention_lib_name(head_dim: int) -> str:
+  return f"libsimply_b200_attn_hd{head_dim}.so"
+
+
+def build_attention(head_dim: int, verbose: bool = True, force: bool = False) -> str:
+  """Compiles the tensor-core attention kernels for one head size; returns the library's path."""
+  if head_dim % 16 or not 16 <= head_dim <= 256:
+    raise KernelBuildError(f"tensor-core attention takes head sizes 16, 32, ..., 256; got {head_dim}")
+  srcs = [os.path.join(CSRC, f) for f in PER_HEAD_DIM]
+  return _build(srcs, attention_lib_name(head_dim), [f"-DSB_HEAD_DIM={head_dim}"], verbose, force)
+
+
+def _build(srcs: list[str], lib_name: str, defines: list[str], verbose: bool, force: bool) -> str:
   out_dir = _build_dir()
-  lib = os.path.join(out_dir, LIB_NAME)
-  stamp = os.path.join(out_dir, "stamp.txt")
-  digest = _digest()
+  lib = os.path.join(out_dir, lib_name)
+  stamp = os.path.join(out_dir, lib_name + ".stamp")
+  digest = _digest(srcs, " ".join(defines))
   if not force and os.path.isfile(lib) and os.path.isfile(stamp):
     with open(stamp) as f:
       if f.read().strip() == digest:
         return lib
   nvcc = _find_nvcc()
-  srcs = sources()
   if verbose:
-    _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out_dir} (first use only)")
+    _say(f"compiling {lib_name} ({len(srcs)} CUDA source(s), sm_100a) into {out_dir} (first use only)")
   t0 = time.time()
   procs = []
   for src in srcs:
-    obj = os.path.join(out_dir, os.path.basename(src)[:-3] + ".o")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
+    obj = os.path.join(out_dir, lib_name[:-3] + "." + os.path.basename(src)[:-3] + ".o")
+    cmd = [nvcc, *NVCC_FLAGS, *defines, "-I", CSRC, "-c", src, "-o", obj]
     procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)))
   objs = []
   pending = list(procs)
@@ -125,7 +146,7 @@ def build(verbose: bool = True, force: bool = False) -> str:
           "-lcudart"]
   r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
   if r.returncode != 0:
-    raise KernelBuildError(f"linking {LIB_NAME} failed:\n{r.stdout.decode(errors='replace')}")
+    raise KernelBuildError(f"linking {lib_name} failed:\n{r.stdout.decode(errors='replace')}")
   os.replace(tmp, lib)
   with open(stamp, "w") as f:
     f.write(digest)
@@ -135,9 +156,22 @@ def build(verbose: bool = True, force: bool = False) -> str:
 
 
 def load() -> ctypes.CDLL:
-  """Builds if needed and loads the library; raises if that is not possible."""
+  """Builds if needed and loads the core library; raises if that is not possible."""
   global _lib
   with _lock:
     if _lib is None:
       _lib = ctypes.CDLL(build())
     return _lib
+
+
+_attention_libs: dict[int, ctypes.CDLL] = {}
+
+
+def load_attention(head_dim: int) -> ctypes.CDLL:
+  """Builds if needed and loads the attention library of one head size."""
+  with _lock:
+    lib = _attention_libs.get(head_dim)
+    if lib is None:
+      lib = ctypes.CDLL(build_attention(head_dim))
+      _attention_libs[head_dim] = lib
+    return lib

@@ -76,6 +76,13 @@ class CudaOps:
       raise KernelError(f"kernels are built for sm_100a; this device is sm_{major}{minor}")
     self._declare()
     self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+    self._attn_fns: dict[int, tuple] = {}
+    # bfloat16 attention runs on tensor cores where the shape allows; False forces the general kernel.
+    self.tensor_core_attention = True
+    # Split-key attention: about this many (sequence, chunk) items per kv head are aimed for;
+    # decode_chunk > 0 fixes the chunk length instead (a multiple of 64).
+    self.decode_target_items = 148 * 4
+    self.decode_chunk = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
@@ -131,10 +138,87 @@ class CudaOps:
 
   # ---- checks ---------------------------------------------------------------
   def check_attention(self, head_dim: int, num_heads: int, num_kv_heads: int) -> None:
+    """Refuses shapes no kernel takes; compiles the tensor-core kernels of this head size."""
     if head_dim <= 0 or head_dim % 2 or head_dim > 512:
       raise KernelError(f"attention kernels take even head sizes up to 512, got {head_dim}")
     if num_heads % num_kv_heads:
       raise KernelError(f"{num_heads} query heads are no multiple of {num_kv_heads} key/value heads")
+    if self._uses_tensor_core_attention(head_dim, num_heads // num_kv_heads):
+      self._attention_lib(head_dim)
+
+  def _uses_tensor_core_attention(self, head_dim: int, group: int) -> bool:
+    return (self.dtype == torch.bfloat16 and self.tensor_core_attention and head_dim % 16 == 0
+            and head_dim <= 256 and group <= 64)
+
+  def _attention_lib(self, head_dim: int):
+    fns = self._attn_fns.get(head_dim)
+    if fns is None:
+      lib = build.load_attention(head_dim)
+      c_int, c_float, c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+      prefill = getattr(lib, f"sb_attn_prefill_hd{head_dim}")
+      prefill.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                          c_float, c_int, c_void, c_int, c_void, c_void]
+      prefill.restype = c_int
+      decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
+      decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
+                         c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void,
+                         c_void, c_void, c_void]
+      decode.restype = c_int
+      fns = self._attn_fns[head_dim] = (prefill, decode)
+    return fns
+
+  def _attention_plan(self, ctx: Any, window: int | None, group: int) -> dict:
+    """Work lists of the two tensor-core kernels for this step, per (window, group).
+
+    Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
+    split-key kernel: their keys are cut into chunks at multiples of `chunk` of the
+    absolute position, one work item per chunk.  The others are cut into tiles of
+    64 // group tokens for the prefill kernel, heaviest tile first.
+    """
+    key = ("attention_plan", window, group)
+    plan = ctx.memo.get(key)
+    if plan is not None:
+      return plan
+    cu_q, q_start = ctx.host["cu_q"], ctx.host["q_start"].astype(np.int64)
+    q_len = np.diff(cu_q).astype(np.int64)
+    small = q_len * group <= 16
+    tokens_per_tile = 64 // group
+    num_seqs = len(q_len)
+    pre = []
+    for b in np.nonzero(~small)[0]:
+      for i0 in range(0, int(q_len[b]), tokens_per_tile):
+        last = int(q_start[b]) + min(i0 + tokens_per_tile, int(q_len[b]))
+        first = max(int(q_start[b]) + i0 - window + 1, 0) if window else 0
+        pre.append((last - first, int(b), i0))
+    pre.sort(key=lambda x: -x[0])
+    prefill_items = np.array([(b, i0) for _, b, i0 in pre], dtype=np.int32).reshape(-1, 2)
+    kv_hi = q_start + q_len
+    kv_lo = np.maximum(q_start - window + 1, 0) if window else np.zeros_like(q_start)
+    kv_lo = kv_lo // 64 * 64
+    dec = np.nonzero(small)[0]
+    chunk = 64
+    if len(dec):
+      total = int((kv_hi[dec] - kv_lo[dec]).sum())
+      chunk = self.decode_chunk or int(min(max(-(-total // self.decode_target_items) + 63 >> 6 << 6, 64), 4096))
+    split_start = np.zeros(num_seqs, dtype=np.int32)
+    split_count = np.zeros(num_seqs, dtype=np.int32)
+    dec_items = []
+    for b in dec:
+      first, last = int(kv_lo[b]) // chunk, (int(kv_hi[b]) - 1) // chunk
+      split_start[b] = len(dec_items)
+      split_count[b] = last - first + 1
+      dec_items += [(int(b), c) for c in range(first, last + 1)]
+    decode_items = np.array(dec_items, dtype=np.int32).reshape(-1, 2)
+    flat = np.concatenate([prefill_items.reshape(-1), decode_items.reshape(-1), split_start, split_count])
+    dev = torch.from_numpy(flat).to(self.device, non_blocking=True)
+    n_pre, n_dec = prefill_items.size, decode_items.size
+    plan = dict(
+        num_prefill=len(prefill_items), num_decode=len(decode_items), chunk=chunk,
+        rows_max=int((q_len[dec] * group).max()) if len(dec) else 0,
+        prefill_items=dev[:n_pre], decode_items=dev[n_pre:n_pre + n_dec],
+        split_start=dev[n_pre + n_dec:n_pre + n_dec + num_seqs], split_count=dev[n_pre + n_dec + num_seqs:])
+    ctx.memo[key] = plan
+    return plan
 
   # ---- dense ----------------------------------------------------------------
   def embed(self, table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
@@ -278,6 +362,30 @@ class CudaOps:
                       window: int | None) -> torch.Tensor:
     t = q.shape[0]
     out = self._new(t, num_heads * head_dim, dtype=q.dtype)
+    group = num_heads // num_kv_heads
+    if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
+      prefill, decode = self._attention_lib(head_dim)
+      plan = self._attention_plan(ctx, window, group)
+      common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
+                _ptr(ctx.q_start))
+      sizes = (num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window or 0))
+      if plan["num_prefill"]:
+        rc = prefill(*common, _ptr(out), *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
+                     _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_attn_prefill: {_STATUS.get(rc, rc)}")
+      if plan["num_decode"]:
+        n = plan["num_decode"] * num_kv_heads * plan["rows_max"]
+        part_o = self._new(n * head_dim, dtype=torch.float32)
+        part_ml = self._new(n * 2, dtype=torch.float32)
+        rc = decode(*common, _ptr(ctx.token_seq), _ptr(out), t, *sizes, _ptr(plan["decode_items"]),
+                    plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), plan["rows_max"],
+                    _ptr(plan["split_start"]), _ptr(plan["split_count"]), _ptr(self.err), self._stream())
+        self.launches += 2
+        if rc:
+          raise KernelError(f"sb_attn_decode: {_STATUS.get(rc, rc)}")
+      return out
     self._call("sb_paged_attention_generic", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
                block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
                num_kv_heads, head_dim, ctx.page_size, storage.shape[0], float(logit_softcap),

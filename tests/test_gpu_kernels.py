@@ -233,6 +233,46 @@ def run_attention(ops, q, sc, hq, hkv, dh, cap, window):
                              head_dim=dh, logit_softcap=cap, window=window)
 
 
+@pytest.fixture
+def general_bf16(table):
+  """The bfloat16 table with the tensor-core attention switched off (the general kernel runs)."""
+  ops = table[torch.bfloat16]
+  ops.tensor_core_attention = False
+  yield ops
+  ops.tensor_core_attention = True
+
+
+@pytest.mark.parametrize("hq,hkv,dh,ps,window,cap", ATTN_CASES)
+def test_paged_attention_general_kernel_bfloat16(general_bf16, hq, hkv, dh, ps, window, cap):
+  ops, ref = general_bf16, ReferenceOps(torch.bfloat16)
+  sc = make_scenario(SEQS, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=torch.bfloat16,
+                     device="cuda", ops=ops, seed=5)
+  q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 1.5).to(torch.bfloat16).cuda()
+  got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+  ops.check_errors()
+  close(got, run_attention(ref, q, sc, hq, hkv, dh, cap, window), torch.bfloat16, 2.0)
+
+
+@pytest.mark.parametrize("chunk", [64, 128, 0])
+@pytest.mark.parametrize("hq,hkv,dh,ps,window,cap", ATTN_CASES)
+def test_split_key_attention_chunks(table, chunk, hq, hkv, dh, ps, window, cap):
+  """Only short entries (the split-key kernel), long histories, several chunk lengths."""
+  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
+  group = hq // hkv
+  seqs = [(1000, 1), (0, 1), (63, 1), (64, 16 // group), (700, 2 if group <= 8 else 1), (129, 1)]
+  sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=torch.bfloat16,
+                     device="cuda", ops=ops, seed=6)
+  q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 1.5).to(torch.bfloat16).cuda()
+  ops.decode_chunk = chunk
+  try:
+    got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+  finally:
+    ops.decode_chunk = 0
+  ops.check_errors()
+  assert torch.isfinite(got).all()
+  close(got, run_attention(ref, q, sc, hq, hkv, dh, cap, window), torch.bfloat16, 2.0)
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("hq,hkv,dh,ps,window,cap", ATTN_CASES)
 def test_paged_attention_random(table, dtype, hq, hkv, dh, ps, window, cap):
