@@ -1,0 +1,326 @@
+"""Benchmark: Gemma 2 2B shape, random bfloat16 weights, one B200.
+
+  python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with every
+sequence ending at the full context (8,192 cached tokens), timed on the device over K
+decode steps that run back to back from CUDA graphs.  `e2e` is the same through the
+public entry point (`Engine.add_request` / `Engine.step`), host tokens in and out, one
+host round trip per step.  `prefill` is one 2,048-token prompt in one step; `points`
+holds decode at batch 1 and 64; `roofline` relates the decode step's bytes (every weight
+once, plus the cache of the live requests) to the measured copy bandwidth.
+
+A step reads 5.2 GB of weights and 0.65 GB of cache per sequence, far more than the
+126 MB L2, so no L2 flush is needed between timed steps ("inputs larger than L2").
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.isfile(path):
+    try:
+      with open(path) as f:
+        d = json.load(f)
+      peaks = {k: float(d[k]) for k in FALLBACK_PEAKS if k in d}
+      if "hbm_gbs" in peaks and "bf16_tflops" in peaks:
+        peaks.setdefault("bf16_tflops_sustained", peaks["bf16_tflops"])
+        return peaks, "measured"
+    except (ValueError, KeyError, TypeError):
+      pass
+  return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+  """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+  QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+           "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+  def __init__(self):
+    self.rows = []
+    self.proc = None
+    self.thread = None
+
+  def start(self):
+    try:
+      self.proc = subprocess.Popen(
+          ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+      return
+    self.thread = threading.Thread(target=self._read, daemon=True)
+    self.thread.start()
+
+  def _read(self):
+    for line in self.proc.stdout:
+      parts = [p.strip() for p in line.split(",")]
+      if len(parts) == 6:
+        self.rows.append(parts)
+
+  def stop(self):
+    if self.proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    clocks = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+    return {
+        "sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+        "sm_max_mhz": max((int(r[1]) for r in self.rows if r[1].isdigit()), default=None),
+        "reasons": reasons,
+        "samples": len(self.rows),
+    }
+
+
+def model_numbers(cfg, layers):
+  """Bytes and FLOPs of the model from its config (layers may be fewer than the config's)."""
+  d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+  hq, hkv, dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+  per_layer = d * (hq + 2 * hkv) * dh + hq * dh * d + 3 * d * f + 4 * d
+  params = layers * per_layer + v * d + d
+  return {"per_layer_params": per_layer, "params": params, "weight_bytes": 2 * params,
+          "kv_bytes_per_token_layer": 2 * hkv * dh * 2}
+
+
+def decode_bytes(cfg, layers, batch, context):
+  n = model_numbers(cfg, layers)
+  types = cfg.resolved_layer_types()[:layers]
+  kv = 0
+  for t in types:
+    seen = min(context, cfg.sliding_window) if t == "sliding_attention" else context
+    kv += seen * n["kv_bytes_per_token_layer"]
+  return n["weight_bytes"] + batch * kv
+
+
+def prefill_flops(cfg, layers, tokens):
+  d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+  hq, hkv, dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+  linear = 2 * tokens * (d * (hq + 2 * hkv) * dh + hq * dh * d + 3 * d * f)
+  types = cfg.resolved_layer_types()[:layers]
+  attn = 0
+  for t in types:
+    w = cfg.sliding_window if t == "sliding_attention" else tokens
+    pairs = sum(min(i + 1, w) for i in range(tokens))
+    attn += 4 * dh * hq * pairs
+  return layers * linear + attn + 2 * d * v
+
+
+def reference_arm(args):
+  """The reference cannot run here: it needs JAX, which is not installed and cannot be
+  (no network); its attention kernel is a TPU Pallas kernel."""
+  why = "google-deepmind/simply needs jax, orbax and a TPU Pallas kernel; none can be installed offline here"
+  try:
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    import jax  # noqa: F401
+    why = "jax is importable but the reference's paged attention is a TPU-only Pallas kernel"
+  except Exception:
+    pass
+  print(json.dumps({"impl": "reference", "unavailable": why}))
+  return 0
+
+
+def time_decode(engine, torch, batch, context, steps, warmup, seed):
+  """Device time of `steps` decode steps at `batch`, the last one ending at `context` cached
+  tokens.  Returns (ms per step, kernel launches per step)."""
+  import numpy as np
+  from simply_b200 import StepEntry
+
+  rng = np.random.default_rng(seed)
+  vocab = engine.model.spec.vocab_size
+  start = context - steps - warmup
+  slots = [engine.open_request(f"bench{seed}_{i}") for i in range(batch)]
+  chunk = 2048
+  for slot in slots:
+    done = 0
+    while done < start:
+      n = min(chunk, start - done)
+      engine.step_raw([StepEntry(slot, rng.integers(0, vocab, n).tolist(), ())])
+      done += n
+  runner = engine._decode_runner
+  params = engine.ops.pack_sample_params([0.0] * batch, [-1] * batch, [1.0] * batch, list(range(batch)),
+                                         [start + 1] * batch)
+  last = rng.integers(0, vocab, batch).tolist()
+  toks = runner.run(slots, last, params, warmup)  # captures the graph, warms up
+  params[:, 5] += warmup
+  # Timed: `steps` replays back to back; events bracket exactly these.
+  torch.cuda.synchronize()
+  launches0 = engine.ops.launches
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  toks = runner.run(slots, toks[-1].tolist(), params, steps)
+  e1.record()
+  torch.cuda.synchronize()
+  ms = e0.elapsed_time(e1) / steps
+  launches = (engine.ops.launches - launches0) / steps
+  engine.ops.check_errors()
+  for slot in slots:
+    engine.close_request(slot)
+  return ms, launches
+
+
+def main(argv=None):
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=32)
+  ap.add_argument("--warmup", type=int, default=4)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--preset", default="gemma2-2b")
+  ap.add_argument("--batch", type=int, default=8)
+  ap.add_argument("--context", type=int, default=0, help="0: the preset's max_position_embeddings")
+  ap.add_argument("--layers", type=int, default=0, help="0: all layers of the preset")
+  ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
+  args = ap.parse_args(argv)
+  if args.impl == "reference":
+    return reference_arm(args)
+  if args.gpus != 1:
+    print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+    return 2
+  if args.warmup < 3:
+    args.warmup = 3
+  if not 1 <= args.steps <= 60:
+    print("bench.py: --steps must be between 1 and 60 (one burst of graph replays)")
+    return 2
+
+  import numpy as np
+  import torch
+
+  from simply_b200 import Engine, EngineConfig, SamplingParams, StepEntry, preset
+
+  peaks, peaks_from = load_peaks()
+  cfg = preset(args.preset)
+  full_layers = cfg.num_hidden_layers
+  layers = args.layers or full_layers
+  if layers != full_layers:
+    cfg = cfg.replace(num_hidden_layers=layers, layer_types=cfg.resolved_layer_types()[:layers])
+  context = args.context or cfg.max_position_embeddings
+  max_batch = 8 if args.skip_points else 64
+  max_batch = max(max_batch, args.batch)
+  ec = EngineConfig(activation_dtype="bfloat16", page_size=64, batch_size=max_batch, max_seq_len=context,
+                    max_cache_tokens=max_batch * context, max_num_issue_tokens=2048, intermediate_steps=1)
+  t0 = time.time()
+  engine = Engine.from_config(cfg, seed=0, engine_config=ec, matrix_std=0.02, scale_std=0.0)
+  torch.cuda.synchronize()
+  setup_s = time.time() - t0
+
+  sampler = ClockSampler()
+  sampler.start()
+
+  # ---- decode, device-timed ----------------------------------------------------------
+  ms_step, launches = time_decode(engine, torch, args.batch, context, args.steps, args.warmup, seed=1)
+  value = args.batch / (ms_step * 1e-3)
+  points = {}
+  if not args.skip_points:
+    for b in (1, 64):
+      ms_b, _ = time_decode(engine, torch, b, context, args.steps, args.warmup, seed=10 + b)
+      points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+      points[f"decode_b{b}_ms"] = round(ms_b, 4)
+      points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, layers, b, context) / (ms_b * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+
+  # ---- prefill: one 2,048-token prompt in one step --------------------------------------
+  rng = np.random.default_rng(5)
+  p_tokens = min(2048, context)
+  prompt = rng.integers(0, cfg.vocab_size, p_tokens).tolist()
+  times = []
+  for i in range(3 + 5):
+    slot = engine.open_request(f"prefill{i}")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    engine.step_raw([StepEntry(slot, prompt, (p_tokens - 1,))])
+    e1.record()
+    torch.cuda.synchronize()
+    if i >= 3:
+      times.append(e0.elapsed_time(e1))
+    engine.close_request(slot)
+  prefill_ms = float(np.median(times))
+  flops = prefill_flops(cfg, layers, p_tokens)
+  prefill = {"value": round(p_tokens / (prefill_ms * 1e-3), 1), "tokens": p_tokens, "ms": round(prefill_ms, 3),
+             "frac": round(flops / (prefill_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)}
+
+  # ---- end to end through the public entry point ------------------------------------------
+  start = context - args.steps - args.warmup
+  prompts = [rng.integers(0, cfg.vocab_size, start).tolist() for _ in range(args.batch)]
+  sp = SamplingParams(temperature=0.0, max_decode_steps=args.steps + args.warmup, stop_token_ids=())
+  requests = [engine.add_request(p, sp) for p in prompts]
+  # All prompts in one step, so that every request starts to decode at the same step.
+  engine.scheduler.max_num_issue_tokens = args.batch * context
+  while any(not r.is_decoding for r in requests):
+    engine.step()  # prompt portions (untimed)
+  for _ in range(args.warmup - 1):
+    engine.step()
+  torch.cuda.synchronize()
+  t0 = time.perf_counter()
+  e2e_steps = 0
+  while engine.has_unfinished() and e2e_steps < args.steps:
+    engine.step()
+    e2e_steps += 1
+  torch.cuda.synchronize()
+  e2e_s = time.perf_counter() - t0
+  while engine.has_unfinished():
+    engine.step()
+  e2e_value = args.batch * e2e_steps / e2e_s
+  runner = engine._decode_runner
+  g = next(iter(runner.graphs.values()))
+  h2d = int(g.meta.numel() * 4)
+  d2h = int(args.batch * 4)
+
+  clocks = sampler.stop()
+  step_bytes = decode_bytes(cfg, layers, args.batch, context)
+  achieved = step_bytes / (ms_step * 1e-3) / 1e9
+  n = model_numbers(cfg, layers)
+  out = {
+      "metric": "decode tok/s @ batch 8, 8192-token context (Gemma 2 2B, 1 B200)",
+      "value": round(value, 1),
+      "unit": "tokens/s",
+      "n_gpus": 1,
+      "steps": args.steps,
+      "warmup": args.warmup,
+      "ms_per_step": round(ms_step, 4),
+      "higher_is_better": True,
+      "scaling": "weak",
+      "vs_baseline": None,
+      "dtype": "bf16",
+      "data": "synthetic: random bf16 weights N(0, 0.02) seed 0, uniform random token ids",
+      "impl": "ours",
+      "config": {
+          "model": args.preset, "layers": layers, "layers_full": full_layers, "width": cfg.hidden_size,
+          "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+          "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size, "window": cfg.sliding_window,
+          "global_batch": args.batch, "seq_len": context, "page_size": 64, "parallelism": "1 GPU",
+          "l2": "inputs larger than L2", "peaks": peaks_from, "params": n["params"],
+      },
+      "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+              "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+      "gpu_launches": int(round(launches * args.steps)),
+      "prefill": prefill,
+      "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                   "frac": round(achieved / peaks["hbm_gbs"], 4)},
+      "points": points,
+      "clocks": clocks,
+      "setup_s": round(setup_s, 1),
+  }
+  print(json.dumps(out))
+  return 0
+
+
+if __name__ == "__main__":
+  sys.exit(main())

@@ -32,6 +32,10 @@ class EngineConfig:
   max_num_issue_tokens: int = 0
   # Replay decode-only steps from CUDA graphs.
   use_cuda_graphs: bool = True
+  # Decode steps that run in a row without the host in between (the reference's flag of
+  # the same name, simply/serving/common_flags.py:84-86); a request that ends inside such a
+  # burst drops the tokens sampled after its end.  At most 64.
+  intermediate_steps: int = 1
   # Fill freed pages with NaN so that a read of a page the request does not own shows.
   poison_freed_pages: bool = False
 

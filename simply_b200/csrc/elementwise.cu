@@ -380,3 +380,38 @@ extern "C" int sb_soft_cap(float* x, float cap, long long n, cudaStream_t stream
   SB_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Between two decode steps that run without the host in between (the reference's
+// on-device decode loop, simply/utils/ragged_paged_attention.py:2064-2102): the
+// sampled token becomes the next input, every position moves on by one, and the
+// token is recorded in history[step, :].
+//   sample_params: [B, 6] int32 words, word 5 is the position of the token to sample.
+// ---------------------------------------------------------------------------
+__global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
+                                      int* __restrict__ positions, int* __restrict__ q_start,
+                                      int* __restrict__ sample_params, int* __restrict__ history,
+                                      int* __restrict__ step_counter, int batch) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int step = *step_counter;
+  if (i < batch) {
+    const int tok = sampled[i];
+    history[(size_t)step * batch + i] = tok;
+    token_ids[i] = tok;
+    positions[i] += 1;
+    q_start[i] += 1;
+    sample_params[i * 6 + 5] += 1;
+  }
+  __syncthreads();  // launched as a single block: every thread has read the counter by now
+  if (threadIdx.x == 0) *step_counter = step + 1;
+}
+
+extern "C" int sb_decode_advance(const int* sampled, int* token_ids, int* positions, int* q_start,
+                                 int* sample_params, int* history, int* step_counter, int batch,
+                                 cudaStream_t stream) {
+  if (batch <= 0 || batch > 1024) return -10;  // one block of 1024 threads covers the batch
+  decode_advance_kernel<<<1, 1024, 0, stream>>>(sampled, token_ids, positions, q_start, sample_params, history,
+                                                step_counter, batch);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

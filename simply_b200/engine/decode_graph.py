@@ -1,0 +1,217 @@
+"""Decode steps replayed from CUDA graphs, several in a row without the host in between.
+
+A step in which every live request brings exactly one token always launches the
+same kernels; only a few integers change.  The runner keeps those integers in one
+static device buffer, captures the whole step (model, sampling, and a tiny kernel
+that turns the sampled tokens into the next step's inputs) in a CUDA graph per
+(batch size, length bucket), and replays it.  A burst of n replays needs one
+host-to-device copy before and one device-to-host copy after, which is the
+reference's on-device decode loop (`continue_decode` with `intermediate_steps`,
+simply/utils/ragged_paged_attention.py:2064-2102, simply/serving/common_flags.py:84-86)
+without a tracing compiler.
+
+The pages for all n tokens of every request are taken before the burst, so block
+tables do not change inside it.  The split-key attention work lists cover the keys
+of the whole burst; chunks with nothing visible at a given step come out empty.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+
+from simply_b200.engine.batch import StepContext
+from simply_b200.parts.attention import PagedAttention
+
+
+def graphable(model: Any) -> bool:
+  """Graphs are used when every mixer is the built-in paged attention (other mixers may
+  read host-side metadata that a replay does not refresh)."""
+  return all(type(b.mixer) is PagedAttention for b in model.blocks.values())
+
+
+@dataclasses.dataclass
+class _Graph:
+  graph: torch.cuda.CUDAGraph
+  meta: torch.Tensor  # static int32 buffer on the device
+  host: torch.Tensor  # pinned mirror
+  views: dict[str, tuple[int, int]]  # name -> (offset, size) in words
+  plans: dict[tuple, dict]
+  sampled: torch.Tensor
+  history: torch.Tensor
+  host_history: torch.Tensor  # pinned
+  step_fn: Any
+  captured: bool
+  batch: int
+  bucket: int
+  chunk: int
+  launches: int
+
+
+class DecodeRunner:
+
+  MAX_BURST = 64
+
+  def __init__(self, engine: Any):
+    self.engine = engine
+    self.ops = engine.ops
+    self.graphs: dict[tuple[int, int], _Graph] = {}
+    self.attn_kinds = sorted(
+        {(b.mixer.window, b.mixer.num_heads // b.mixer.num_kv_heads) for b in engine.model.blocks.values()},
+        key=lambda k: (k[0] or 0, k[1]))
+    self.stream = torch.cuda.Stream(device=engine.device)
+
+  # ---- layout of the static buffer -----------------------------------------------
+  def _layout(self, batch: int, bucket: int, chunk: int) -> tuple[dict, dict, int]:
+    cache = self.engine.cache
+    views, off = {}, 0
+
+    def take(name, size):
+      nonlocal off
+      views[name] = (off, size)
+      off += size
+
+    for name in ("token_ids", "positions", "token_seq", "q_start", "slots", "logit_rows"):
+      take(name, batch)
+    take("cu_q", batch + 1)
+    take("step_counter", 1)
+    take("sample_params", batch * 6)
+    for gi, g in enumerate(cache.groups):
+      take(f"table{gi}", batch * g.max_pages_per_seq)
+    items_per_seq = {}
+    for window, group in self.attn_kinds:
+      span = min(bucket, window + self.MAX_BURST + 64) if window else bucket
+      per_seq = -(-span // chunk) + 1
+      items_per_seq[(window, group)] = per_seq
+      take(f"items{window}_{group}", batch * per_seq * 2)
+      take(f"split_start{window}_{group}", batch)
+      take(f"split_count{window}_{group}", batch)
+    return views, items_per_seq, off
+
+  def _prepare(self, batch: int, bucket: int) -> _Graph:
+    """Static buffers and the step closure for one (batch, bucket); nothing runs yet."""
+    eng, ops = self.engine, self.ops
+    chunk = ops.decode_chunk_for(batch, bucket)
+    views, items_per_seq, words = self._layout(batch, bucket, chunk)
+    meta = torch.zeros(words, dtype=torch.int32, device=eng.device)
+    host = torch.zeros(words, dtype=torch.int32).pin_memory()
+
+    def view(name):
+      o, n = views[name]
+      return meta[o:o + n]
+
+    block_tables = [view(f"table{gi}").view(batch, g.max_pages_per_seq)
+                    for gi, g in enumerate(eng.cache.groups)]
+    ctx = StepContext(
+        ops=ops, num_tokens=batch, num_seqs=batch, token_ids=view("token_ids"), positions=view("positions"),
+        token_seq=view("token_seq"), cu_q=view("cu_q"), q_start=view("q_start"), slots=view("slots"),
+        block_tables=block_tables, logit_rows=view("logit_rows"), max_q_len=1, max_kv_len=bucket,
+        page_size=eng.cache.page_size)
+    plans = {}
+    for (window, group), per_seq in items_per_seq.items():
+      plans[(window, group)] = dict(
+          num_prefill=0, num_decode=batch * per_seq, chunk=chunk, rows_max=group,
+          prefill_items=None, decode_items=view(f"items{window}_{group}"),
+          split_start=view(f"split_start{window}_{group}"), split_count=view(f"split_count{window}_{group}"))
+    sampled = torch.zeros(batch, dtype=torch.int32, device=eng.device)
+    history = torch.zeros(self.MAX_BURST, batch, dtype=torch.int32, device=eng.device)
+    host_history = torch.zeros(self.MAX_BURST, batch, dtype=torch.int32).pin_memory()
+
+    def one_step():
+      ctx.memo = {("attention_plan", w, gr): p for (w, gr), p in plans.items()}
+      logits = eng.model.forward(ctx, eng.caches)
+      ops.sample_device(logits, view("sample_params").view(batch, 6), sampled)
+      ops.decode_advance(sampled, view("token_ids"), view("positions"), view("q_start"),
+                         view("sample_params"), history, view("step_counter"))
+
+    g = _Graph(torch.cuda.CUDAGraph(), meta, host, views, plans, sampled, history, host_history, one_step,
+               False, batch, bucket, chunk, 0)
+    self._fill_constants(g)
+    return g
+
+  def _first_step_and_capture(self, g: _Graph) -> None:
+    """Runs the burst's first step eagerly on the capture stream (this also sets up library
+    handles and kernel attributes), then records the same step into the graph.  Recording
+    executes nothing, so the state stays where the eager step left it."""
+    current = torch.cuda.current_stream(self.engine.device)
+    self.stream.wait_stream(current)
+    with torch.cuda.stream(self.stream):
+      g.step_fn()
+      self.stream.synchronize()
+      before = self.ops.launches
+      with torch.cuda.graph(g.graph, stream=self.stream):
+        g.step_fn()
+      g.launches = self.ops.launches - before
+    self.stream.synchronize()
+    g.captured = True
+
+  def _fill_constants(self, g: _Graph) -> None:
+    b = g.batch
+    h = g.host.numpy()
+
+    def put(name, values):
+      o, n = g.views[name]
+      h[o:o + n] = np.asarray(values, dtype=np.int32).reshape(-1)
+
+    put("token_seq", np.arange(b))
+    put("logit_rows", np.arange(b))
+    put("cu_q", np.arange(b + 1))
+    put("step_counter", [0])
+
+  # ---- running -----------------------------------------------------------------------
+  def run(self, slots: Sequence[int], last_tokens: Sequence[int], sample_params: np.ndarray,
+          steps: int) -> np.ndarray:
+    """Decodes `steps` tokens for every slot; returns the sampled tokens [steps, batch].
+
+    `last_tokens[i]` is the not yet cached last token of slot i; `sample_params` is the
+    [batch, 6] word table of csrc/sampling.cu with the position of the first token to sample.
+    """
+    eng = self.engine
+    cache = eng.cache
+    batch = len(slots)
+    if not 1 <= steps <= self.MAX_BURST:
+      raise ValueError(f"a decode burst has 1..{self.MAX_BURST} steps, got {steps}")
+    lengths = np.array([cache.length(s) for s in slots], dtype=np.int64)
+    cache.extend([(s, steps) for s in slots])
+    bucket = 1024
+    while bucket < int(lengths.max()) + steps:
+      bucket *= 2
+    key = (batch, bucket)
+    g = self.graphs.get(key)
+    if g is None:
+      g = self.graphs[key] = self._prepare(batch, bucket)
+    h = g.host.numpy()
+
+    def put(name, values):
+      o, n = g.views[name]
+      h[o:o + n] = np.asarray(values, dtype=np.int32).reshape(-1)
+
+    put("token_ids", last_tokens)
+    put("positions", lengths)
+    put("q_start", lengths)
+    put("slots", slots)
+    put("step_counter", [0])
+    put("sample_params", sample_params)
+    for gi, grp in enumerate(cache.groups):
+      put(f"table{gi}", grp.tables[np.asarray(slots)])
+    for (window, group), plan in g.plans.items():
+      per_seq = plan["num_decode"] // batch
+      items, start, count = self.ops.static_decode_plan(lengths, steps, window, g.chunk, per_seq)
+      put(f"items{window}_{group}", items)
+      put(f"split_start{window}_{group}", start)
+      put(f"split_count{window}_{group}", count)
+    g.meta.copy_(g.host, non_blocking=True)
+    replays = steps
+    if not g.captured:
+      self._first_step_and_capture(g)
+      replays -= 1
+    for _ in range(replays):
+      g.graph.replay()
+    g.host_history[:steps].copy_(g.history[:steps], non_blocking=True)
+    torch.cuda.current_stream(eng.device).synchronize()
+    self.ops.launches += g.launches * replays
+    eng.num_steps += steps
+    return g.host_history[:steps].numpy().copy()

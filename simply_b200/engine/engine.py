@@ -81,6 +81,11 @@ class Engine:
                                max_seq_len=ec.max_seq_len, eos_ids=eos_ids)
     self._next_id = 0
     self.num_steps = 0
+    self._decode_runner = None
+    if ec.use_cuda_graphs and self.device.type == "cuda" and hasattr(self.ops, "decode_advance"):
+      from simply_b200.engine import decode_graph
+      if decode_graph.graphable(self.model):
+        self._decode_runner = decode_graph.DecodeRunner(self)
 
   # ---- construction ---------------------------------------------------------
   @classmethod
@@ -158,6 +163,8 @@ class Engine:
     finished = list(plan.failed)
     if not plan.entries:
       return finished
+    if self._decode_runner is not None and all(e.request.is_decoding for e in plan.entries):
+      return finished + self._decode_burst(plan)
     entries = []
     samplers = []
     for e in plan.entries:
@@ -179,6 +186,32 @@ class Engine:
       for r, t in zip(samplers, tokens.tolist()):
         sampled[r.request_id] = t
     return finished + self.scheduler.commit(plan, sampled)
+
+  def _decode_burst(self, plan: StepPlan) -> list[Request]:
+    """A step (or `intermediate_steps` steps in a row) in which every entry decodes one token,
+    replayed from a CUDA graph."""
+    requests = [e.request for e in plan.entries]
+    steps = max(1, min(self.engine_config.intermediate_steps, self._decode_runner.MAX_BURST))
+    for r in requests:
+      steps = min(steps, r.params.max_decode_steps - len(r.output),
+                  self.engine_config.max_seq_len - len(r.tokens))
+    steps = max(steps, 1)
+    while steps > 1 and self.cache.pages_short([(r.slot, steps) for r in requests]):
+      steps //= 2
+    params = self.ops.pack_sample_params(
+        [r.params.temperature for r in requests], [r.params.top_k for r in requests],
+        [r.params.top_p for r in requests], [r.params.seed for r in requests],
+        [len(r.tokens) for r in requests])
+    tokens = self._decode_runner.run([r.slot for r in requests], [r.tokens[-1] for r in requests],
+                                     params, steps)
+    finished: list[Request] = []
+    for i in range(steps):
+      live = [e for e in plan.entries if e.request.status.value == "running"]
+      step_plan = StepPlan(live, [], [])
+      sampled = {e.request.request_id: int(tokens[i, requests.index(e.request)]) for e in live}
+      finished += self.scheduler.commit(step_plan, sampled)
+    # Requests that are still live hold exactly the tokens the burst cached.
+    return finished
 
   def generate(self, prompts: Sequence[Sequence[int]],
                params: SamplingParams | Sequence[SamplingParams] | None = None

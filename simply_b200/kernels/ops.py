@@ -38,6 +38,7 @@ _STATUS = {
     -7: "head size outside the attention kernel's range",
     -8: "query heads are no multiple of key/value heads",
     -9: "shape outside the weight-streaming product's range",
+    -10: "batch outside the decode-advance kernel's range",
 }
 
 
@@ -108,6 +109,7 @@ class CudaOps:
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void],
+        "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
     }
     for name, argtypes in protos.items():
       fn = getattr(self.lib, name)
@@ -166,6 +168,38 @@ class CudaOps:
       decode.restype = c_int
       fns = self._attn_fns[head_dim] = (prefill, decode)
     return fns
+
+  def decode_chunk_for(self, batch: int, kv_len: int) -> int:
+    """Chunk length of split-key attention for `batch` sequences of up to `kv_len` keys."""
+    if self.decode_chunk:
+      return self.decode_chunk
+    return int(min(max(-(-batch * kv_len // self.decode_target_items) + 63 >> 6 << 6, 64), 4096))
+
+  @staticmethod
+  def static_decode_plan(q_start: np.ndarray, steps: int, window: int | None, chunk: int,
+                         items_per_seq: int) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Work list of the split-key kernel for a decode burst replayed from a CUDA graph.
+
+    Every sequence gets exactly `items_per_seq` items, so the launch has a fixed size:
+    the chunks that hold keys between the lowest key visible at the first step and the
+    highest at the last step, then fillers (sequence -1).  A chunk that holds nothing
+    visible at some step of the burst yields an empty partial result there.
+    Returns (items [B * items_per_seq, 2], split_start [B], split_count [B]).
+    """
+    b = len(q_start)
+    items = np.full((b, items_per_seq, 2), -1, dtype=np.int32)
+    count = np.zeros(b, dtype=np.int32)
+    for i, qs in enumerate(q_start.astype(np.int64)):
+      lo = max(int(qs) - window + 1, 0) // 64 * 64 if window else 0
+      first, last = lo // chunk, (int(qs) + steps - 1) // chunk
+      n = last - first + 1
+      if n > items_per_seq:
+        raise KernelError(f"decode burst needs {n} chunks per sequence, the graph holds {items_per_seq}")
+      items[i, :n, 0] = i
+      items[i, :n, 1] = np.arange(first, last + 1)
+      count[i] = n
+    start = (np.arange(b) * items_per_seq).astype(np.int32)
+    return items.reshape(-1, 2), start, count
 
   def _attention_plan(self, ctx: Any, window: int | None, group: int) -> dict:
     """Work lists of the two tensor-core kernels for this step, per (window, group).
@@ -395,7 +429,14 @@ class CudaOps:
   # ---- sampling -------------------------------------------------------------
   def sample(self, logits: torch.Tensor, temperature, top_k, top_p, seed, position) -> torch.Tensor:
     """One token per row of float32 logits; the other arguments are host sequences."""
-    r, vocab = logits.shape
+    params = self.pack_sample_params(temperature, top_k, top_p, seed, position)
+    dev_params = torch.from_numpy(params).to(self.device, non_blocking=True)
+    return self.sample_device(logits, dev_params)
+
+  @staticmethod
+  def pack_sample_params(temperature, top_k, top_p, seed, position) -> np.ndarray:
+    """The [R, 6] int32 words the sampling kernel reads (see csrc/sampling.cu)."""
+    r = len(temperature)
     params = np.zeros((r, 6), dtype=np.int32)
     params[:, 0] = np.asarray(temperature, dtype=np.float32).view(np.int32)
     params[:, 1] = np.asarray(top_k, dtype=np.int32)
@@ -404,7 +445,17 @@ class CudaOps:
     params[:, 3] = (seeds & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)
     params[:, 4] = (seeds >> np.uint64(32)).astype(np.uint32).view(np.int32)
     params[:, 5] = np.asarray(position, dtype=np.int32)
-    dev_params = torch.from_numpy(params).to(self.device, non_blocking=True)
-    out = self._new(r, dtype=torch.int32)
+    return params
+
+  def sample_device(self, logits: torch.Tensor, dev_params: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Sampling with the parameter words already on the device."""
+    r, vocab = logits.shape
+    if out is None:
+      out = self._new(r, dtype=torch.int32)
     self._call("sb_sample", _ptr(logits.contiguous()), _ptr(dev_params), _ptr(out), r, vocab)
     return out
+
+  def decode_advance(self, sampled, token_ids, positions, q_start, sample_params, history, step_counter) -> None:
+    self._call("sb_decode_advance", _ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(q_start),
+               _ptr(sample_params), _ptr(history), _ptr(step_counter), sampled.numel())

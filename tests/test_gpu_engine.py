@@ -1,0 +1,139 @@
+"""Generation through the public entry point on the GPU, against the plain model."""
+
+import numpy as np
+import pytest
+import torch
+
+from simply_b200 import Engine, EngineConfig, SamplingParams, StepEntry
+from tests.plain.gemma2_plain import PlainGemma2
+from tests.tiny_models import write_tiny
+from tests.tolerances import assert_logits_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+  root = tmp_path_factory.mktemp("models")
+  return {w: write_tiny(w, root, "bfloat16") for w in ("a", "b")}
+
+
+def engine_for(folder, dtype, **kw):
+  kw.setdefault("page_size", 8)
+  kw.setdefault("batch_size", 4)
+  kw.setdefault("max_seq_len", 256)
+  return Engine.from_folder(folder, EngineConfig(activation_dtype=dtype, **kw))
+
+
+def prompts_for(plain, lengths, seed=1):
+  rng = np.random.default_rng(seed)
+  return [rng.integers(0, plain.cfg["vocab_size"], n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("which,lengths,steps", [("a", (5, 11, 17), 8), ("b", (1, 23, 40), 12)])
+def test_greedy_generation_float32_equals_plain(folders, which, lengths, steps):
+  plain = PlainGemma2(folders[which])
+  prompts = prompts_for(plain, lengths)
+  want = [plain.greedy(p, steps) for p in prompts]
+  for graphs in (True, False):
+    eng = engine_for(folders[which], "float32", use_cuda_graphs=graphs)
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=steps, stop_token_ids=()))
+    eng.ops.check_errors()
+    assert [r.output_token_ids for r in got] == want
+    assert all(r.finish_reason == "max_decode_steps" for r in got)
+    eng.cache.check_invariants()
+
+
+def test_temperature_sampling_float32_equals_plain(folders):
+  plain = PlainGemma2(folders["b"])
+  prompts = prompts_for(plain, (1, 23, 40))
+  want = [plain.sample(p, 12, 0.8, 3) for p in prompts]
+  # prompts cut into portions of 7 and mixed with decoding requests in one batch
+  eng = engine_for(folders["b"], "float32", max_num_issue_tokens=7)
+  got = eng.generate(prompts, SamplingParams(temperature=0.8, seed=3, max_decode_steps=12, stop_token_ids=()))
+  assert [r.output_token_ids for r in got] == want
+  # top-k and top-p as well
+  want = [plain.sample(p, 6, 1.3, 11, top_k=20, top_p=0.9) for p in prompts]
+  got = eng.generate(prompts, SamplingParams(temperature=1.3, seed=11, top_k=20, top_p=0.9, max_decode_steps=6,
+                                             stop_token_ids=()))
+  assert [r.output_token_ids for r in got] == want
+
+
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_bfloat16_generation_follows_the_plain_model(folders, which):
+  """bfloat16 may turn a near-tie, so compare teacher-forced: the engine's greedy choice at
+  every step must be a token whose plain logit is within the bfloat16 bound of the best."""
+  plain = PlainGemma2(folders[which])
+  prompts = prompts_for(plain, (9, 30, 70))
+  eng = engine_for(folders[which], "bfloat16")
+  got = eng.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=24, stop_token_ids=()))
+  eng.ops.check_errors()
+  for p, r in zip(prompts, got):
+    full = p + r.output_token_ids
+    logits = plain.forward(full[:-1])
+    scale = np.abs(logits).max()
+    for i, tok in enumerate(r.output_token_ids):
+      row = logits[len(p) - 1 + i]
+      assert row.max() - row[tok] <= 2 * 3e-2 * scale, (i, tok, int(row.argmax()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_and_bursts_equal_plain_steps(folders, dtype):
+  plain = PlainGemma2(folders["b"])
+  prompts = prompts_for(plain, (3, 18, 33, 50), seed=4)
+  sp = SamplingParams(temperature=0.7, seed=5, max_decode_steps=40, stop_token_ids=())
+  outs = []
+  for graphs, burst in ((False, 1), (True, 1), (True, 7)):
+    eng = engine_for(folders["b"], dtype, use_cuda_graphs=graphs, intermediate_steps=burst)
+    outs.append([r.output_token_ids for r in eng.generate(prompts, sp)])
+    eng.ops.check_errors()
+    eng.cache.check_invariants()
+  assert outs[0] == outs[1] == outs[2]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_logits(folders, dtype):
+  """One request decoded token by token far beyond the window and over many pages, logits
+  compared at every step."""
+  plain = PlainGemma2(folders["a"])
+  toks = prompts_for(plain, (200,), seed=8)[0]
+  want = plain.forward(toks)
+  eng = engine_for(folders["a"], dtype, page_size=4, max_cache_tokens=256)
+  slot = eng.open_request()
+  rows = [eng.step_raw([StepEntry(slot, toks[:3], (0, 1, 2))])]
+  rows += [eng.step_raw([StepEntry(slot, [t], (0,))]) for t in toks[3:]]
+  eng.ops.check_errors()
+  assert_logits_close(torch.cat(rows).cpu().numpy(), want, dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folders, dtype):
+  plain = PlainGemma2(folders["b"])
+  for n in (1, 2, 3):
+    toks = prompts_for(plain, (n,), seed=20 + n)[0]
+    eng = engine_for(folders["b"], dtype)
+    slot = eng.open_request()
+    got = eng.step_raw([StepEntry(slot, toks, tuple(range(n)))]).cpu().numpy()
+    assert_logits_close(got, plain.forward(toks), dtype, f"{n} tokens")
+
+
+def test_preemption_gives_the_same_tokens(folders):
+  """So few pages that decoding requests must take pages from the youngest; the output is
+  what an engine with room produces."""
+  plain = PlainGemma2(folders["b"])
+  prompts = prompts_for(plain, (20, 25, 30), seed=9)
+  sp = SamplingParams(temperature=0.9, seed=2, max_decode_steps=30, stop_token_ids=())
+  roomy = engine_for(folders["b"], "float32").generate(prompts, sp)
+  tight_engine = engine_for(folders["b"], "float32", max_cache_tokens=120)
+  tight = tight_engine.generate(prompts, sp)
+  assert [r.output_token_ids for r in tight] == [r.output_token_ids for r in roomy]
+  assert sum(r.num_preemptions for r in tight) > 0
+  tight_engine.cache.check_invariants()
+  assert tight_engine.cache.min_free_pages() == tight_engine.cache.num_pages
+
+
+def test_engine_refuses_without_cuda_kernels(monkeypatch):
+  from simply_b200.kernels import ops as ops_mod
+  monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+  with pytest.raises(ops_mod.KernelError, match="no CPU path"):
+    ops_mod.CudaOps(torch.bfloat16)
