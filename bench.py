@@ -177,6 +177,47 @@ def time_decode(engine, torch, batch, context, steps, warmup, seed):
   return ms, launches
 
 
+def profile_step(engine, torch, cfg, args, context):
+  """One eager step for a profiler.  The cache is made to *hold* the context without
+  computing it (attention time does not depend on the cache's contents), so that few
+  launches precede the profiled ones."""
+  import numpy as np
+  from simply_b200 import StepEntry
+
+  rng = np.random.default_rng(3)
+  if args.profile == "decode":
+    slots = [engine.open_request(f"p{i}") for i in range(args.batch)]
+    engine.cache.extend([(s, context - 2) for s in slots])
+    entries = [StepEntry(s, [int(rng.integers(0, cfg.vocab_size))], (0,)) for s in slots]
+  else:
+    slot = engine.open_request("p")
+    n = min(2048, context - 1)
+    entries = [StepEntry(slot, rng.integers(0, cfg.vocab_size, n).tolist(), (n - 1,))]
+
+  def step():
+    logits = engine.step_raw(entries)
+    engine.ops.sample(logits, [0.0] * len(entries), [-1] * len(entries), [1.0] * len(entries),
+                      [0] * len(entries), [1] * len(entries))
+
+  if args.profile == "prefill":
+    step()  # warm-up on the same slot is not possible for a prompt; use a second request
+    engine.close_request(entries[0].slot)
+    slot = engine.open_request("p2")
+    entries = [StepEntry(slot, entries[0].tokens, entries[0].want)]
+  else:
+    step()
+    entries = [StepEntry(e.slot, e.tokens, e.want) for e in entries]
+  torch.cuda.synchronize()
+  torch.cuda.profiler.start()
+  step()
+  torch.cuda.synchronize()
+  torch.cuda.profiler.stop()
+  engine.ops.check_errors()
+  print(f"profiled one {args.profile} step: {len(entries)} entries, context {context}, "
+        f"{cfg.num_hidden_layers} layers")
+  return 0
+
+
 def main(argv=None):
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
@@ -188,6 +229,9 @@ def main(argv=None):
   ap.add_argument("--context", type=int, default=0, help="0: the preset's max_position_embeddings")
   ap.add_argument("--layers", type=int, default=0, help="0: all layers of the preset")
   ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
+  ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                  help="run ONE eager step of this kind between cudaProfilerStart/Stop and exit "
+                       "(for ncu --profile-from-start off); prints no benchmark line")
   args = ap.parse_args(argv)
   if args.impl == "reference":
     return reference_arm(args)
@@ -220,6 +264,9 @@ def main(argv=None):
   engine = Engine.from_config(cfg, seed=0, engine_config=ec, matrix_std=0.02, scale_std=0.0)
   torch.cuda.synchronize()
   setup_s = time.time() - t0
+
+  if args.profile:
+    return profile_step(engine, torch, cfg, args, context)
 
   sampler = ClockSampler()
   sampler.start()

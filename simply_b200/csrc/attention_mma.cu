@@ -14,10 +14,10 @@
 //    to shared memory once serves the whole group.  Four warps own 16 rows each and
 //    walk the key tiles (64 keys) with an online softmax.
 //  * decode (at most 16 query rows per sequence and kv head, i.e. one or a few new
-//    tokens): the keys are cut into chunks at fixed absolute positions; a block owns
-//    one chunk, its four warps split every 64-key tile four ways, merge, and store a
-//    partial result (max, sum, normalised output) that `combine` merges over chunks in
-//    a fixed order.
+//    tokens): the keys are cut into chunks at fixed absolute positions; a persistent
+//    grid draws (chunk, kv head) pairs from a counter; a block's warps split every key
+//    tile between them, merge, and store a partial result (max, sum, normalised
+//    output) that `combine` merges over chunks in a fixed order.
 // Keys and values come from the paged cache through the block table with 16-byte
 // cp.async copies; rows outside what the request holds are zero-filled, never read.
 #include <float.h>
@@ -102,29 +102,38 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Brings keys [tile, tile + BN) of (sequence b, kv head m) to shared memory; positions
-// outside [kv_lo, kv_hi) and pages the request does not hold are zero-filled.
-__device__ __forceinline__ void load_kv_tile(const AttnParams& p, bf16* sk, bf16* sv, int tile, int kv_lo,
-                                             int kv_hi, int b, int m) {
+// Brings keys [tile, tile + TILE) of (sequence b, kv head m) to shared memory; positions
+// outside [kv_lo, kv_hi) and pages the request does not hold are zero-filled.  The block
+// first works out where each of the TILE rows lives (one block-table lookup per row, into
+// `row_src`, TILE entries of shared memory), then copies 16 bytes per thread and turn.
+// Ends with the copies issued, not committed.  Contains one __syncthreads.
+template <int TILE, int THREADS>
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, bf16* sk, bf16* sv, long long* row_src,
+                                             int tile, int kv_lo, int kv_hi, int b, int m) {
   const size_t head_stride = (size_t)p.page_size * DH;
   const size_t v_offset = (size_t)p.num_kv_heads * head_stride;
-  for (int i = threadIdx.x; i < BN * CPR; i += NT) {
-    const int row = i / CPR, c = i - row * CPR;
+  for (int row = threadIdx.x; row < TILE; row += THREADS) {
     const int j = tile + row;
-    bool valid = j >= kv_lo && j < kv_hi;
-    long long page = 0;
-    if (valid) {
-      page = p.block_table[(size_t)b * p.max_pages + j / p.page_size];
-      if (page < 0 || page >= p.num_pages) {
-        if (c == 0) atomicOr(p.err, SB_ERR_BAD_PAGE);
-        valid = false;
-        page = 0;
-      }
+    long long src = -1;
+    if (j >= kv_lo && j < kv_hi) {
+      const int page_index = j / p.page_size;
+      const long long page = p.block_table[(size_t)b * p.max_pages + page_index];
+      if (page < 0 || page >= p.num_pages)
+        atomicOr(p.err, SB_ERR_BAD_PAGE);
+      else
+        src = (long long)(((size_t)page * 2 * p.num_kv_heads + m) * head_stride +
+                          (size_t)(j - page_index * p.page_size) * DH);
     }
-    const bf16* src = p.cache + ((size_t)page * 2 * p.num_kv_heads + m) * head_stride +
-                      (size_t)(valid ? j % p.page_size : 0) * DH + c * 8;
-    cp_async16(sk + row * PITCH + c * 8, src, valid);
-    cp_async16(sv + row * PITCH + c * 8, src + v_offset, valid);
+    row_src[row] = src;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < TILE * CPR; i += THREADS) {
+    const int row = i / CPR, c = i - row * CPR;
+    const long long src = row_src[row];
+    const bool valid = src >= 0;
+    const bf16* g = p.cache + (valid ? src : 0) + c * 8;
+    cp_async16(sk + row * PITCH + c * 8, g, valid);
+    cp_async16(sv + row * PITCH + c * 8, g + v_offset, valid);
   }
 }
 
@@ -226,6 +235,7 @@ __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [64][PITCH]
   bf16* sk = sq + 64 * PITCH;                    // [2][BN][PITCH]
   bf16* sv = sk + 2 * BN * PITCH;                // [2][BN][PITCH]
+  __shared__ long long row_src[2][BN];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int b = p.items[2 * blockIdx.x], i0 = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
   const int group = p.num_q_heads / p.num_kv_heads;
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
   const int kv_hi = p1 + 1;
   const int tile0 = (lo / BN) * BN;
   const int n_tiles = (kv_hi - tile0 + BN - 1) / BN;
-  load_kv_tile(p, sk, sv, tile0, kv_lo, kv_hi, b, m);
+  load_kv_tile<BN, NT>(p, sk, sv, row_src[0], tile0, kv_lo, kv_hi, b, m);
   cp_async_commit();
 
   const int ra = warp * 16 + g, rb = ra + 8;
@@ -260,8 +270,8 @@ __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it & 1;
     if (it + 1 < n_tiles) {
-      load_kv_tile(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, tile0 + (it + 1) * BN, kv_lo,
-                   kv_hi, b, m);
+      load_kv_tile<BN, NT>(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, row_src[stage ^ 1],
+                           tile0 + (it + 1) * BN, kv_lo, kv_hi, b, m);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -294,110 +304,130 @@ __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Decode: grid (items, kv heads), 128 threads; a block owns one chunk of keys.
+// Decode: a persistent grid; blocks draw (item, kv head) pairs from a counter until none is
+// left, so short and long chunks balance out.  A block has DEC_BN / 16 warps; warp w owns
+// keys [16 w, 16 w + 16) of every tile.  Tiles of 32 keys for head sizes above 128 keep the
+// block's shared memory below half an SM's, so two blocks run side by side and one's start
+// and end overlap the other's stream of tiles.
 // ---------------------------------------------------------------------------------------
-template <int STAGES>
-__global__ void __launch_bounds__(NT) attn_decode_kernel(const AttnParams p) {
+constexpr int DEC_BN = DH > 128 ? 32 : 64;
+constexpr int DEC_WARPS = DEC_BN / 16;
+constexpr int DEC_NT = DEC_WARPS * 32;
+constexpr int DEC_STAGES = 3;
+
+__global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p, int* work_counter, int total_work) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [16][PITCH]
-  bf16* sk = sq + 16 * PITCH;                    // [STAGES][BN][PITCH]
-  bf16* sv = sk + STAGES * BN * PITCH;           // [STAGES][BN][PITCH]
+  bf16* sk = sq + 16 * PITCH;                    // [STAGES][DEC_BN][PITCH]
+  bf16* sv = sk + DEC_STAGES * DEC_BN * PITCH;   // [STAGES][DEC_BN][PITCH]
+  __shared__ int s_work;
+  __shared__ long long row_src[DEC_STAGES][DEC_BN];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-  const int b = p.items[2 * blockIdx.x], chunk_index = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
-  if (b < 0) return;  // filler item of a fixed-size launch
   const int group = p.num_q_heads / p.num_kv_heads;
-  const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
-  const int rows_valid = q_len * group;  // <= 16 by the host's routing
-  const int kv_lo = p.window > 0 ? max(qs - p.window + 1, 0) : 0;
-  const int kv_hi = qs + q_len;
-  const int begin = max(chunk_index * p.chunk, (kv_lo / BN) * BN);
-  const int end = min((chunk_index + 1) * p.chunk, kv_hi);
-  const int n_tiles = end > begin ? (end - begin + BN - 1) / BN : 0;
+  for (;;) {
+    if (threadIdx.x == 0) s_work = atomicAdd(work_counter, 1);
+    __syncthreads();
+    const int work = s_work;
+    __syncthreads();  // everyone has read s_work; shared memory of the last item is free
+    if (work >= total_work) break;
+    const int item = work / p.num_kv_heads, m = work - item * p.num_kv_heads;
+    const int b = p.items[2 * item], chunk_index = p.items[2 * item + 1];
+    if (b < 0) continue;  // filler item of a fixed-size work list
+    const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
+    const int rows_valid = q_len * group;  // <= 16 by the host's routing
+    const int kv_lo = p.window > 0 ? max(qs - p.window + 1, 0) : 0;
+    const int kv_hi = qs + q_len;
+    const int begin = max(chunk_index * p.chunk, (kv_lo / 64) * 64);
+    const int end = min((chunk_index + 1) * p.chunk, kv_hi);
+    const int n_tiles = end > begin ? (end - begin + DEC_BN - 1) / DEC_BN : 0;
 
-  for (int i = threadIdx.x; i < 16 * CPR; i += NT) {
-    const int row = i / CPR, c = i - row * CPR;
-    const bool valid = row < rows_valid;
-    const int tok = valid ? row / group : 0, h = m * group + (valid ? row % group : 0);
-    cp_async16(sq + row * PITCH + c * 8, p.q + ((size_t)(row0 + tok) * p.num_q_heads + h) * DH + c * 8, valid);
-  }
+    for (int i = threadIdx.x; i < 16 * CPR; i += DEC_NT) {
+      const int row = i / CPR, c = i - row * CPR;
+      const bool valid = row < rows_valid;
+      const int tok = valid ? row / group : 0, h = m * group + (valid ? row % group : 0);
+      cp_async16(sq + row * PITCH + c * 8, p.q + ((size_t)(row0 + tok) * p.num_q_heads + h) * DH + c * 8, valid);
+    }
 #pragma unroll
-  for (int st = 0; st < STAGES - 1; ++st) {
-    if (st < n_tiles)
-      load_kv_tile(p, sk + st * BN * PITCH, sv + st * BN * PITCH, begin + st * BN, kv_lo, end, b, m);
-    cp_async_commit();
-  }
-  const int pos_a = g < rows_valid ? qs + g / group : -1;
-  const int pos_b = g + 8 < rows_valid ? qs + (g + 8) / group : -1;
-  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-  float o[DH / 8][4];
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+      if (st < n_tiles)  // uniform over the block
+        load_kv_tile<DEC_BN, DEC_NT>(p, sk + st * DEC_BN * PITCH, sv + st * DEC_BN * PITCH, row_src[st],
+                                     begin + st * DEC_BN, kv_lo, end, b, m);
+      cp_async_commit();
+    }
+    const int pos_a = g < rows_valid ? qs + g / group : -1;
+    const int pos_b = g + 8 < rows_valid ? qs + (g + 8) / group : -1;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[DH / 8][4];
 #pragma unroll
-  for (int d = 0; d < DH / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    for (int d = 0; d < DH / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
-  for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it % STAGES;
-    cp_async_wait<STAGES - 2>();
-    __syncthreads();  // tile `it` has landed; everyone is done with tile it - 1
-    if (it + STAGES - 1 < n_tiles) {
-      const int st = (it + STAGES - 1) % STAGES;
-      load_kv_tile(p, sk + st * BN * PITCH, sv + st * BN * PITCH, begin + (it + STAGES - 1) * BN, kv_lo, end, b, m);
+    for (int it = 0; it < n_tiles; ++it) {
+      const int stage = it % DEC_STAGES;
+      cp_async_wait<DEC_STAGES - 2>();
+      __syncthreads();  // tile `it` has landed; everyone is done with tile it - 1
+      if (it + DEC_STAGES - 1 < n_tiles) {
+        const int st = (it + DEC_STAGES - 1) % DEC_STAGES;
+        load_kv_tile<DEC_BN, DEC_NT>(p, sk + st * DEC_BN * PITCH, sv + st * DEC_BN * PITCH, row_src[st],
+                                     begin + (it + DEC_STAGES - 1) * DEC_BN, kv_lo, end, b, m);
+      }
+      cp_async_commit();
+      float s[2][4];
+      scores<2>(s, sq, sk + stage * DEC_BN * PITCH, warp * 16);
+      softmax_pv<2>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, begin + it * DEC_BN + warp * 16, p.cap, p.window,
+                    sv + stage * DEC_BN * PITCH, warp * 16);
     }
-    cp_async_commit();
-    float s[2][4];
-    scores<2>(s, sq, sk + stage * BN * PITCH, warp * 16);
-    softmax_pv<2>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, begin + it * BN + warp * 16, p.cap, p.window,
-                  sv + stage * BN * PITCH, warp * 16);
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
-  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
-  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    cp_async_wait<0>();
+    __syncthreads();
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
 
-  // Merge the four warps (each saw a quarter of every tile) through shared memory.
-  float* wm = reinterpret_cast<float*>(sk);  // [4][16] max, [4][16] sum, then [4][rows_valid][DH]
-  float* wl = wm + 64;
-  float* wo = wl + 64;
-  if (t == 0) {
-    wm[warp * 16 + g] = m_a;
-    wm[warp * 16 + g + 8] = m_b;
-    wl[warp * 16 + g] = l_a;
-    wl[warp * 16 + g + 8] = l_b;
-  }
-  if (g < rows_valid) {
-#pragma unroll
-    for (int d = 0; d < DH / 8; ++d) {
-      wo[((size_t)warp * rows_valid + g) * DH + d * 8 + 2 * t] = o[d][0];
-      wo[((size_t)warp * rows_valid + g) * DH + d * 8 + 2 * t + 1] = o[d][1];
+    // Merge the warps (each saw its share of every tile) through shared memory.
+    float* wm = reinterpret_cast<float*>(sk);  // [W][16] max, [W][16] sum, then [W][rows_valid][DH]
+    float* wl = wm + DEC_WARPS * 16;
+    float* wo = wl + DEC_WARPS * 16;
+    if (t == 0) {
+      wm[warp * 16 + g] = m_a;
+      wm[warp * 16 + g + 8] = m_b;
+      wl[warp * 16 + g] = l_a;
+      wl[warp * 16 + g + 8] = l_b;
     }
-  }
-  if (g + 8 < rows_valid) {
+    if (g < rows_valid) {
 #pragma unroll
-    for (int d = 0; d < DH / 8; ++d) {
-      wo[((size_t)warp * rows_valid + g + 8) * DH + d * 8 + 2 * t] = o[d][2];
-      wo[((size_t)warp * rows_valid + g + 8) * DH + d * 8 + 2 * t + 1] = o[d][3];
-    }
-  }
-  __syncthreads();
-  const size_t pidx = (size_t)blockIdx.x * p.num_kv_heads + m;
-  for (int i = threadIdx.x; i < rows_valid * DH; i += NT) {
-    const int r = i / DH, d = i - r * DH;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wm[w * 16 + r]);
-    float num = 0.f, den = 0.f;
-    if (mx != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float sc = fast_exp2(wm[w * 16 + r] - mx);
-        num += sc * wo[((size_t)w * rows_valid + r) * DH + d];
-        den += sc * wl[w * 16 + r];
+      for (int d = 0; d < DH / 8; ++d) {
+        wo[((size_t)warp * rows_valid + g) * DH + d * 8 + 2 * t] = o[d][0];
+        wo[((size_t)warp * rows_valid + g) * DH + d * 8 + 2 * t + 1] = o[d][1];
       }
     }
-    p.part_o[(pidx * p.rows_max + r) * DH + d] = den > 0.f ? num / den : 0.f;
-    if (d == 0) {
-      p.part_ml[(pidx * p.rows_max + r) * 2] = mx;
-      p.part_ml[(pidx * p.rows_max + r) * 2 + 1] = den;
+    if (g + 8 < rows_valid) {
+#pragma unroll
+      for (int d = 0; d < DH / 8; ++d) {
+        wo[((size_t)warp * rows_valid + g + 8) * DH + d * 8 + 2 * t] = o[d][2];
+        wo[((size_t)warp * rows_valid + g + 8) * DH + d * 8 + 2 * t + 1] = o[d][3];
+      }
+    }
+    __syncthreads();
+    const size_t pidx = (size_t)item * p.num_kv_heads + m;
+    for (int i = threadIdx.x; i < rows_valid * DH; i += DEC_NT) {
+      const int r = i / DH, d = i - r * DH;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, wm[w * 16 + r]);
+      float num = 0.f, den = 0.f;
+      if (mx != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+          const float sc = fast_exp2(wm[w * 16 + r] - mx);
+          num += sc * wo[((size_t)w * rows_valid + r) * DH + d];
+          den += sc * wl[w * 16 + r];
+        }
+      }
+      p.part_o[(pidx * p.rows_max + r) * DH + d] = den > 0.f ? num / den : 0.f;
+      if (d == 0) {
+        p.part_ml[(pidx * p.rows_max + r) * 2] = mx;
+        p.part_ml[(pidx * p.rows_max + r) * 2 + 1] = den;
+      }
     }
   }
 }
@@ -419,22 +449,31 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   const int r = (tkn - cu_q[b]) * group + h % group;
   const int first = split_start[b];
   float mx = -INFINITY;
-  for (int s = 0; s < count; ++s)
+  for (int s = lane; s < count; s += 32)
     mx = fmaxf(mx, part_ml[(((size_t)(first + s) * num_kv_heads + m) * rows_max + r) * 2]);
+  mx = warp_max(mx);
   float acc[DH / 32 + 1];
 #pragma unroll
   for (int i = 0; i < DH / 32 + 1; ++i) acc[i] = 0.f;
   float den = 0.f;
-  for (int s = 0; s < count; ++s) {
-    const size_t pidx = ((size_t)(first + s) * num_kv_heads + m) * rows_max + r;
-    const float ms = part_ml[pidx * 2], ls = part_ml[pidx * 2 + 1];
-    if (ls <= 0.f) continue;
-    const float w = ls * fast_exp2(ms - mx);
-    den += w;
+  for (int s0 = 0; s0 < count; s0 += 32) {
+    // Lane j weighs chunk s0 + j; the chunks are then added in ascending order.
+    float w = 0.f;
+    if (s0 + lane < count) {
+      const size_t pidx = ((size_t)(first + s0 + lane) * num_kv_heads + m) * rows_max + r;
+      const float ms = part_ml[pidx * 2], ls = part_ml[pidx * 2 + 1];
+      w = ls > 0.f ? ls * fast_exp2(ms - mx) : 0.f;
+    }
+    const int n = min(32, count - s0);
+    for (int j = 0; j < n; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      const size_t pidx = ((size_t)(first + s0 + j) * num_kv_heads + m) * rows_max + r;
+      den += wj;
 #pragma unroll
-    for (int i = 0; i < DH / 32 + 1; ++i) {
-      const int d = lane + 32 * i;
-      if (d < DH) acc[i] += w * part_o[pidx * DH + d];
+      for (int i = 0; i < DH / 32 + 1; ++i) {
+        const int d = lane + 32 * i;
+        if (d < DH) acc[i] = fmaf(wj, part_o[pidx * DH + d], acc[i]);
+      }
     }
   }
   const float inv = den > 0.f ? 1.0f / den : 0.f;
@@ -446,10 +485,10 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   }
 }
 
-constexpr int DECODE_STAGES = 3;
 constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BN) * PITCH * sizeof(bf16);
-constexpr size_t DECODE_SMEM_KV = (size_t)(16 + 2 * DECODE_STAGES * BN) * PITCH * sizeof(bf16);
-constexpr size_t DECODE_SMEM_MERGE = 16 * PITCH * sizeof(bf16) + (128 + 4 * 16 * DH) * sizeof(float);
+constexpr size_t DECODE_SMEM_KV = (size_t)(16 + 2 * DEC_STAGES * DEC_BN) * PITCH * sizeof(bf16);
+constexpr size_t DECODE_SMEM_MERGE =
+    16 * PITCH * sizeof(bf16) + (size_t)(2 * DEC_WARPS * 16 + DEC_WARPS * 16 * DH) * sizeof(float);
 constexpr size_t DECODE_SMEM = DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE;
 
 }  // namespace
@@ -485,30 +524,40 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
 // Split-key attention for sequences with at most 16 query rows per kv head, and the merge.
 // items: [num_items, 2] (sequence or -1, chunk index); chunk: keys per chunk, a multiple of 64;
 // part_o / part_ml: scratch of num_items * Hkv * rows_max * (DH | 2) floats;
+// work_counter: one int of scratch, zeroed here on the stream before the launch;
 // split_start / split_count: per sequence, its range of items (count 0: not handled here).
 extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int* block_table, int max_pages,
                                      const int* cu_q, const int* q_start, const int* token_seq, void* out,
                                      int num_tokens, int num_q_heads, int num_kv_heads, int page_size,
                                      int num_pages, float cap, int window, const int* items, int num_items,
-                                     int chunk, float* part_o, float* part_ml, int rows_max,
-                                     const int* split_start, const int* split_count, int* err,
+                                     int chunk, float* part_o, float* part_ml, int* work_counter,
+                                     int rows_max, const int* split_start, const int* split_count, int* err,
                                      cudaStream_t stream) {
   if (num_items == 0) return 0;
-  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || rows_max > 16 || chunk % BN) return -8;
+  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || rows_max > 16 || chunk % 64) return -8;
   AttnParams p{};
   p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.chunk = chunk; p.part_o = part_o; p.part_ml = part_ml;
   p.rows_max = rows_max; p.err = err;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DECODE_STAGES>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+  static int resident = 0;  // blocks of this kernel the device holds at once
+  if (resident == 0) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)DECODE_SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    int per_sm = 0, sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, DEC_NT, DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    resident = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
   }
-  attn_decode_kernel<DECODE_STAGES><<<dim3(num_items, num_kv_heads), NT, DECODE_SMEM, stream>>>(p);
+  const int total_work = num_items * num_kv_heads;
+  cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  attn_decode_kernel<<<total_work < resident ? total_work : resident, DEC_NT, DECODE_SMEM, stream>>>(
+      p, work_counter, total_work);
   SB_LAUNCH_CHECK();
   const long long rows = (long long)num_tokens * num_q_heads;
   attn_combine_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(

@@ -82,7 +82,7 @@ class CudaOps:
     self.tensor_core_attention = True
     # Split-key attention: about this many (sequence, chunk) items per kv head are aimed for;
     # decode_chunk > 0 fixes the chunk length instead (a multiple of 64).
-    self.decode_target_items = 148 * 4
+    self.decode_target_items = 148 * 2
     self.decode_chunk = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -163,8 +163,8 @@ class CudaOps:
       prefill.restype = c_int
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
-                         c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_void,
-                         c_void, c_void, c_void]
+                         c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_int,
+                         c_void, c_void, c_void, c_void]
       decode.restype = c_int
       fns = self._attn_fns[head_dim] = (prefill, decode)
     return fns
@@ -173,7 +173,12 @@ class CudaOps:
     """Chunk length of split-key attention for `batch` sequences of up to `kv_len` keys."""
     if self.decode_chunk:
       return self.decode_chunk
-    return int(min(max(-(-batch * kv_len // self.decode_target_items) + 63 >> 6 << 6, 64), 4096))
+    return self._chunk_for_keys(batch * kv_len)
+
+  def _chunk_for_keys(self, total_keys: int) -> int:
+    # Chunks are drawn dynamically by a persistent grid, so they only need to be small enough
+    # to balance and large enough to amortise a block's start: 128 to 512 keys.
+    return int(min(max(-(-total_keys // self.decode_target_items) + 63 >> 6 << 6, 128), 512))
 
   @staticmethod
   def static_decode_plan(q_start: np.ndarray, steps: int, window: int | None, chunk: int,
@@ -233,7 +238,7 @@ class CudaOps:
     chunk = 64
     if len(dec):
       total = int((kv_hi[dec] - kv_lo[dec]).sum())
-      chunk = self.decode_chunk or int(min(max(-(-total // self.decode_target_items) + 63 >> 6 << 6, 64), 4096))
+      chunk = self.decode_chunk or self._chunk_for_keys(total)
     split_start = np.zeros(num_seqs, dtype=np.int32)
     split_count = np.zeros(num_seqs, dtype=np.int32)
     dec_items = []
@@ -413,8 +418,10 @@ class CudaOps:
         n = plan["num_decode"] * num_kv_heads * plan["rows_max"]
         part_o = self._new(n * head_dim, dtype=torch.float32)
         part_ml = self._new(n * 2, dtype=torch.float32)
+        counter = self._new(1, dtype=torch.int32)
         rc = decode(*common, _ptr(ctx.token_seq), _ptr(out), t, *sizes, _ptr(plan["decode_items"]),
-                    plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), plan["rows_max"],
+                    plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), _ptr(counter),
+                    plan["rows_max"],
                     _ptr(plan["split_start"]), _ptr(plan["split_count"]), _ptr(self.err), self._stream())
         self.launches += 2
         if rc:
