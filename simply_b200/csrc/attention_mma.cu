@@ -432,57 +432,62 @@ __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p,
   }
 }
 
-// Merges the chunks of every (token, query head): one warp each, chunks in ascending order.
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const int* __restrict__ token_seq, const int* __restrict__ cu_q,
-                                    const int* __restrict__ split_start, const int* __restrict__ split_count,
-                                    bf16* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
-                                    int rows_max) {
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= (long long)num_tokens * num_q_heads) return;
-  const int tkn = (int)(item / num_q_heads), h = (int)(item % num_q_heads);
+// Merges the chunks of every (token, query head): one block each.  Its warps take the
+// chunks in turn (warp w: chunks w, w + 4, ...), then add up in a fixed order.
+constexpr int COMBINE_WARPS = 4;
+constexpr int DPL = (DH + 31) / 32;  // output elements per lane
+
+__global__ void __launch_bounds__(COMBINE_WARPS * 32)
+attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                    const int* __restrict__ split_start, const int* __restrict__ split_count,
+                    bf16* __restrict__ out, int num_q_heads, int num_kv_heads, int rows_max) {
+  __shared__ float s_acc[COMBINE_WARPS][DH];
+  __shared__ float s_den[COMBINE_WARPS];
+  __shared__ float s_max[COMBINE_WARPS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tkn = blockIdx.x / num_q_heads, h = blockIdx.x - tkn * num_q_heads;
   const int b = token_seq[tkn];
   const int count = split_count[b];
   if (count <= 0) return;  // this sequence went through the prefill kernel
   const int group = num_q_heads / num_kv_heads, m = h / group;
   const int r = (tkn - cu_q[b]) * group + h % group;
-  const int first = split_start[b];
+  const size_t base = ((size_t)split_start[b] * num_kv_heads + m) * rows_max + r;
+  const size_t stride = (size_t)num_kv_heads * rows_max;  // from one chunk's partial to the next
   float mx = -INFINITY;
-  for (int s = lane; s < count; s += 32)
-    mx = fmaxf(mx, part_ml[(((size_t)(first + s) * num_kv_heads + m) * rows_max + r) * 2]);
+  for (int s = threadIdx.x; s < count; s += COMBINE_WARPS * 32) mx = fmaxf(mx, part_ml[(base + s * stride) * 2]);
   mx = warp_max(mx);
-  float acc[DH / 32 + 1];
+  if (lane == 0) s_max[warp] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+  float acc[DPL];
 #pragma unroll
-  for (int i = 0; i < DH / 32 + 1; ++i) acc[i] = 0.f;
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
   float den = 0.f;
-  for (int s0 = 0; s0 < count; s0 += 32) {
-    // Lane j weighs chunk s0 + j; the chunks are then added in ascending order.
-    float w = 0.f;
-    if (s0 + lane < count) {
-      const size_t pidx = ((size_t)(first + s0 + lane) * num_kv_heads + m) * rows_max + r;
-      const float ms = part_ml[pidx * 2], ls = part_ml[pidx * 2 + 1];
-      w = ls > 0.f ? ls * fast_exp2(ms - mx) : 0.f;
-    }
-    const int n = min(32, count - s0);
-    for (int j = 0; j < n; ++j) {
-      const float wj = __shfl_sync(0xffffffffu, w, j);
-      const size_t pidx = ((size_t)(first + s0 + j) * num_kv_heads + m) * rows_max + r;
-      den += wj;
+#pragma unroll 4
+  for (int s = warp; s < count; s += COMBINE_WARPS) {
+    const size_t pidx = base + s * stride;
+    const float ms = part_ml[pidx * 2], ls = part_ml[pidx * 2 + 1];
+    const float w = ls > 0.f ? ls * fast_exp2(ms - mx) : 0.f;  // an empty chunk stored zeros
+    den += w;
 #pragma unroll
-      for (int i = 0; i < DH / 32 + 1; ++i) {
-        const int d = lane + 32 * i;
-        if (d < DH) acc[i] = fmaf(wj, part_o[pidx * DH + d], acc[i]);
-      }
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < DH) acc[i] = fmaf(w, part_o[pidx * DH + d], acc[i]);
     }
   }
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < DH) s_acc[warp][d] = acc[i];
+  }
+  if (lane == 0) s_den[warp] = den;
+  __syncthreads();
+  den = (s_den[0] + s_den[1]) + (s_den[2] + s_den[3]);
   const float inv = den > 0.f ? 1.0f / den : 0.f;
   bf16* op = out + ((size_t)tkn * num_q_heads + h) * DH;
-#pragma unroll
-  for (int i = 0; i < DH / 32 + 1; ++i) {
-    const int d = lane + 32 * i;
-    if (d < DH) op[d] = __float2bfloat16_rn(acc[i] * inv);
-  }
+  for (int d = threadIdx.x; d < DH; d += COMBINE_WARPS * 32)
+    op[d] = __float2bfloat16_rn(((s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d])) * inv);
 }
 
 constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BN) * PITCH * sizeof(bf16);
@@ -559,10 +564,9 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
   attn_decode_kernel<<<total_work < resident ? total_work : resident, DEC_NT, DECODE_SMEM, stream>>>(
       p, work_counter, total_work);
   SB_LAUNCH_CHECK();
-  const long long rows = (long long)num_tokens * num_q_heads;
-  attn_combine_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(
-      part_o, part_ml, token_seq, cu_q, split_start, split_count, (bf16*)out, num_tokens, num_q_heads,
-      num_kv_heads, rows_max);
+  attn_combine_kernel<<<(unsigned)(num_tokens * num_q_heads), COMBINE_WARPS * 32, 0, stream>>>(
+      part_o, part_ml, token_seq, cu_q, split_start, split_count, (bf16*)out, num_q_heads, num_kv_heads,
+      rows_max);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -33,6 +33,55 @@ __device__ __forceinline__ float load_scalar(const void* p, int is_f32, int i) {
                 : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
 }
 
+// 16-byte vectors of storage type T: 4 floats or 8 bfloat16, loaded to / stored from float registers.
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ __forceinline__ static void load(const float* p, float* out) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  }
+  __device__ __forceinline__ static void store(float* p, const float* in) {
+    *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
+  }
+};
+template <> struct Vec<bf16> {
+  static constexpr int N = 8;
+  __device__ __forceinline__ static void load(const bf16* p, float* out) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      out[2 * i] = __uint_as_float(w[i] << 16);
+      out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ __forceinline__ static void store(bf16* p, const float* in) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// N consecutive scalars of a vector stored as float32 or bfloat16 (N = 4 or 8, i a multiple of N).
+template <int N>
+__device__ __forceinline__ void load_scalars(const void* p, int is_f32, int i, float* out) {
+  if (is_f32) {
+#pragma unroll
+    for (int k = 0; k < N; k += 4) Vec<float>::load(reinterpret_cast<const float*>(p) + i + k, out + k);
+  } else if (N == 8) {
+    Vec<bf16>::load(reinterpret_cast<const bf16*>(p) + i, out);
+  } else {
+    const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p) + i);
+    out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
+    out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -24,7 +24,19 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   }
   const T* row = table + (size_t)id * width;
   float* o = out + (size_t)t * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
+  constexpr int N = Vec<T>::N;
+  if (width % N == 0) {
+    for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+      float v[N];
+      Vec<T>::load(row + i, v);
+#pragma unroll
+      for (int k = 0; k < N; ++k) v[k] *= scale;
+#pragma unroll
+      for (int k = 0; k < N; k += 4) Vec<float>::store(o + i + k, v + k);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
+  }
 }
 
 extern "C" int sb_embed(const void* table, int table_dtype, const int* ids, float scale, float* out,
@@ -61,14 +73,29 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
     src = 0;
   }
   float* hp = h + (size_t)src * width;
+  constexpr int N = Vec<T>::N;
+  const bool vec = width % N == 0;
+  const float post_one = post_plus_one ? 1.f : 0.f, pre_one = pre_plus_one ? 1.f : 0.f;
   float rstd_b = 1.f;
   if (branch) {
     const T* bp = branch + (size_t)src * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-      float b = to_f32<T>(bp[i]);
-      row[i] = b;
-      ss += b * b;
+    if (vec) {
+      for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+        float b[N];
+        Vec<T>::load(bp + i, b);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          row[i + k] = b[k];
+          ss += b[k] * b[k];
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float b = to_f32<T>(bp[i]);
+        row[i] = b;
+        ss += b * b;
+      }
     }
     if (w_post) {
       ss = block_sum(ss, scratch);
@@ -76,23 +103,59 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
     }
   }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = hp[i];
-    if (branch) {
-      float b = row[i];
-      if (w_post) b = b * rstd_b * (load_scalar(w_post, post_f32, i) + (post_plus_one ? 1.f : 0.f));
-      v += b;
-      if (!rows) hp[i] = v;
+  if (vec) {
+    for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+      float v[N], w[N];
+#pragma unroll
+      for (int k = 0; k < N; k += 4) Vec<float>::load(hp + i + k, v + k);
+      if (branch) {
+        if (w_post) load_scalars<N>(w_post, post_f32, i, w);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          float b = row[i + k];
+          if (w_post) b = b * rstd_b * (w[k] + post_one);
+          v[k] += b;
+        }
+        if (!rows) {
+#pragma unroll
+          for (int k = 0; k < N; k += 4) Vec<float>::store(hp + i + k, v + k);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        row[i + k] = v[k];
+        ss += v[k] * v[k];
+      }
     }
-    row[i] = v;
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float v = hp[i];
+      if (branch) {
+        float b = row[i];
+        if (w_post) b = b * rstd_b * (load_scalar(w_post, post_f32, i) + post_one);
+        v += b;
+        if (!rows) hp[i] = v;
+      }
+      row[i] = v;
+      ss += v * v;
+    }
   }
   if (w_pre) {
     ss = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(ss / (float)width + eps_pre);
     T* yp = y + (size_t)r * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-      yp[i] = from_f32<T>(row[i] * rstd * (load_scalar(w_pre, pre_f32, i) + (pre_plus_one ? 1.f : 0.f)));
+    if (vec) {
+      for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+        float w[N], o[N];
+        load_scalars<N>(w_pre, pre_f32, i, w);
+#pragma unroll
+        for (int k = 0; k < N; ++k) o[k] = row[i + k] * rstd * (w[k] + pre_one);
+        Vec<T>::store(yp + i, o);
+      }
+    } else {
+      for (int i = threadIdx.x; i < width; i += blockDim.x)
+        yp[i] = from_f32<T>(row[i] * rstd * (load_scalar(w_pre, pre_f32, i) + pre_one));
+    }
   }
 }
 
@@ -285,6 +348,48 @@ __global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const float* 
       page = -1;
     }
   }
+  constexpr int N = Vec<T>::N;
+  if (half % N == 0) {
+    // N pairs (j, j + half) per thread and turn, 16-byte loads and stores.
+    const int chunks = half / N;
+    for (int i = threadIdx.x; i < heads * chunks; i += blockDim.x) {
+      const int hh = i / chunks, j = (i - hh * chunks) * N;
+      float a[N], b[N];
+      Vec<T>::load(in + hh * head_dim + j, a);
+      Vec<T>::load(in + hh * head_dim + half + j, b);
+      if (hh < num_q_heads + num_kv_proj && cos_t) {
+        float c[N], sn[N];
+#pragma unroll
+        for (int k = 0; k < N; k += 4) {
+          Vec<float>::load(cos_t + (size_t)t * half + j + k, c + k);
+          Vec<float>::load(sin_t + (size_t)t * half + j + k, sn + k);
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const float ra = a[k] * c[k] - b[k] * sn[k], rb = b[k] * c[k] + a[k] * sn[k];
+          a[k] = ra;
+          b[k] = rb;
+        }
+      }
+      if (hh < num_q_heads) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          a[k] *= q_scale;
+          b[k] *= q_scale;
+        }
+        T* o = q_out + ((size_t)t * num_q_heads + hh) * head_dim;
+        Vec<T>::store(o + j, a);
+        Vec<T>::store(o + half + j, b);
+      } else if (page >= 0) {
+        const int kv = hh < num_q_heads + num_kv_proj ? 0 : 1;
+        const int m = hh - num_q_heads - kv * num_kv_proj;
+        T* o = cache + ((((size_t)page * 2 + kv) * num_kv_proj + m) * page_size + offset) * head_dim;
+        Vec<T>::store(o + j, a);
+        Vec<T>::store(o + half + j, b);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
     const int hh = i / half, j = i - hh * half;
     float a = to_f32<T>(in[hh * head_dim + j]);
@@ -342,6 +447,22 @@ __device__ __forceinline__ float apply_activation(float g, int act) {
 }
 
 template <typename T>
+__global__ void gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden,
+                                            int act, size_t chunks) {
+  constexpr int N = Vec<T>::N;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= chunks) return;
+  const size_t per_row = hidden / N;
+  const size_t t = i / per_row, f = (i - t * per_row) * N;
+  float g[N], u[N];
+  Vec<T>::load(gate_up + t * 2 * hidden + f, g);
+  Vec<T>::load(gate_up + t * 2 * hidden + hidden + f, u);
+#pragma unroll
+  for (int k = 0; k < N; ++k) g[k] = apply_activation(g[k], act) * u[k];
+  Vec<T>::store(z + t * hidden + f, g);
+}
+
+template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden, int act,
                                         size_t n) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -358,10 +479,19 @@ extern "C" int sb_gated_activation(const void* gate_up, int dtype, void* z, int 
   if (n == 0) return 0;
   if (act < 0 || act > 2) return -5;
   const unsigned blocks = (unsigned)((n + 255) / 256);
-  if (dtype == SB_DTYPE_F32)
-    gated_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)z, hidden, act, n);
-  else
-    gated_activation_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)z, hidden, act, n);
+  if (dtype == SB_DTYPE_F32) {
+    if (hidden % 4 == 0)
+      gated_activation_vec_kernel<float><<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(
+          (const float*)gate_up, (float*)z, hidden, act, n / 4);
+    else
+      gated_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)z, hidden, act, n);
+  } else {
+    if (hidden % 8 == 0)
+      gated_activation_vec_kernel<bf16><<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(
+          (const bf16*)gate_up, (bf16*)z, hidden, act, n / 8);
+    else
+      gated_activation_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)z, hidden, act, n);
+  }
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -1,4 +1,4 @@
-// Sampling from float32 logits, one block per row.
+// Sampling from float32 logits.
 //
 // Semantics of simply/utils/sampling_lib.py:472-537:
 //   temperature == 0 or top_k == 1 -> argmax (lowest index on ties)
@@ -99,30 +99,29 @@ __device__ float block_max(float v, float* scratch) {
 
 // params per row (int32 words): temperature (float bits), top_k, top_p (float bits),
 // seed low, seed high, position.
+//
+// Three launches: (1) one block per row finds the row's keep-threshold (0 when neither top-k
+// nor top-p is set: the block leaves at once); (2) `slices` blocks per row each find the best
+// entry of their slice of the vocabulary (plain argmax when greedy, argmax of scaled logit +
+// Gumbel noise otherwise); (3) one warp per row picks the best slice, lowest index on ties.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, const int* __restrict__ params, int* __restrict__ out,
-              int vocab) {
+sample_threshold_kernel(const float* __restrict__ logits, const int* __restrict__ params,
+                        uint32_t* __restrict__ thresholds, int vocab) {
   __shared__ float fscratch[33];
-  __shared__ ArgMax ascratch[33];
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const int* p = params + r * 6;
   const float temperature = __int_as_float(p[0]);
   const int top_k = p[1];
   const float top_p = __int_as_float(p[2]);
-  const uint32_t seed_lo = (uint32_t)p[3], seed_hi = (uint32_t)p[4];
-  const uint32_t position = (uint32_t)p[5];
-
-  if (temperature == 0.f || top_k == 1) {
-    ArgMax best{-FLT_MAX, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = better(best, ArgMax{row[i], i});
-    best = block_argmax(best, ascratch);
-    if (threadIdx.x == 0) out[r] = best.i;
+  const bool greedy = temperature == 0.f || top_k == 1;
+  const bool use_k = !greedy && top_k > 0 && top_k < vocab, use_p = !greedy && top_p < 1.f;
+  if (!use_k && !use_p) {
+    if (threadIdx.x == 0) thresholds[r] = 0;
     return;
   }
-
   uint32_t threshold = 0;  // keep entries whose key >= threshold
-  if (top_k > 0 && top_k < vocab) {
+  if (use_k) {
     // Largest K with count(key >= K) >= top_k: the key of the k-th largest entry.
     for (int bit = 31; bit >= 0; --bit) {
       const uint32_t cand = threshold | (1u << bit);
@@ -132,7 +131,7 @@ sample_kernel(const float* __restrict__ logits, const int* __restrict__ params, 
       if (cnt >= (float)top_k) threshold = cand;
     }
   }
-  if (top_p < 1.f) {
+  if (use_p) {
     float mx = -FLT_MAX;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
       const float s = row[i] / temperature;
@@ -161,29 +160,81 @@ sample_kernel(const float* __restrict__ logits, const int* __restrict__ params, 
     }
     threshold = max(threshold, k2);
   }
+  if (threadIdx.x == 0) thresholds[r] = threshold;
+}
 
+#define SLICE_THREADS 256
+
+__global__ void __launch_bounds__(SLICE_THREADS)
+sample_slice_kernel(const float* __restrict__ logits, const int* __restrict__ params,
+                    const uint32_t* __restrict__ thresholds, ArgMax* __restrict__ partial, int vocab,
+                    int slice_len) {
+  __shared__ ArgMax ascratch[33];
+  const int r = blockIdx.y, slice = blockIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const int* p = params + r * 6;
+  const float temperature = __int_as_float(p[0]);
+  const int top_k = p[1];
+  const int lo = slice * slice_len, hi = min(lo + slice_len, vocab);  // slice_len is a multiple of 4
   ArgMax best{-FLT_MAX, 0x7fffffff};
-  const int blocks4 = (vocab + 3) / 4;
-  for (int blk = threadIdx.x; blk < blocks4; blk += blockDim.x) {
-    uint32_t bits[4];
-    philox4x32_10((uint32_t)blk, position, 0u, 0u, seed_lo, seed_hi, bits);
+  if (temperature == 0.f || top_k == 1) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, ArgMax{row[i], i});
+  } else {
+    const uint32_t threshold = thresholds[r];
+    const uint32_t seed_lo = (uint32_t)p[3], seed_hi = (uint32_t)p[4], position = (uint32_t)p[5];
+    for (int blk = lo / 4 + threadIdx.x; blk * 4 < hi; blk += blockDim.x) {
+      uint32_t bits[4];
+      philox4x32_10((uint32_t)blk, position, 0u, 0u, seed_lo, seed_hi, bits);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = blk * 4 + e;
-      if (i >= vocab) break;
-      const float s = row[i] / temperature;
-      if (order_key(s) < threshold) continue;
-      best = better(best, ArgMax{s + gumbel_from_bits(bits[e]), i});
+      for (int e = 0; e < 4; ++e) {
+        const int i = blk * 4 + e;
+        if (i >= hi) break;
+        const float s = row[i] / temperature;
+        if (order_key(s) < threshold) continue;
+        best = better(best, ArgMax{s + gumbel_from_bits(bits[e]), i});
+      }
     }
   }
   best = block_argmax(best, ascratch);
-  if (threadIdx.x == 0) out[r] = best.i;
+  if (threadIdx.x == 0) partial[(size_t)r * gridDim.x + slice] = best;
+}
+
+__global__ void sample_final_kernel(const ArgMax* __restrict__ partial, int* __restrict__ out, int slices) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  ArgMax best{-FLT_MAX, 0x7fffffff};
+  for (int s = lane; s < slices; s += 32) best = better(best, partial[(size_t)r * slices + s]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax y;
+    y.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+    best = better(best, y);
+  }
+  if (lane == 0) out[r] = best.i;
+}
+
+// scratch: at least num_rows * (1 + 2 * slices) 32-bit words, slices = sb_sample_slices(num_rows, vocab).
+extern "C" int sb_sample_slices(int num_rows, int vocab) {
+  int slices = (4 * 148 + num_rows - 1) / (num_rows > 0 ? num_rows : 1);
+  if (slices > 64) slices = 64;
+  const int most = (vocab + 1023) / 1024;  // at least about a thousand entries per slice
+  if (slices > most) slices = most;
+  return slices < 1 ? 1 : slices;
 }
 
 extern "C" int sb_sample(const float* logits, const int* params, int* out, int num_rows, int vocab,
-                         cudaStream_t stream) {
+                         void* scratch, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  sample_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, params, out, vocab);
+  const int slices = sb_sample_slices(num_rows, vocab);
+  const int slice_len = ((vocab + slices - 1) / slices + 3) / 4 * 4;
+  uint32_t* thresholds = reinterpret_cast<uint32_t*>(scratch);
+  ArgMax* partial = reinterpret_cast<ArgMax*>(thresholds + num_rows + (num_rows & 1));
+  sample_threshold_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, params, thresholds, vocab);
+  SB_LAUNCH_CHECK();
+  sample_slice_kernel<<<dim3(slices, num_rows), SLICE_THREADS, 0, stream>>>(logits, params, thresholds, partial,
+                                                                          vocab, slice_len);
+  SB_LAUNCH_CHECK();
+  sample_final_kernel<<<num_rows, 32, 0, stream>>>(partial, out, slices);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -108,13 +108,15 @@ class CudaOps:
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void],
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
-        "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void],
+        "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
     }
     for name, argtypes in protos.items():
       fn = getattr(self.lib, name)
       fn.argtypes = argtypes
       fn.restype = c_int
+    self.lib.sb_sample_slices.argtypes = [c_int, c_int]
+    self.lib.sb_sample_slices.restype = c_int
 
   def _stream(self):
     return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -460,7 +462,10 @@ class CudaOps:
     r, vocab = logits.shape
     if out is None:
       out = self._new(r, dtype=torch.int32)
-    self._call("sb_sample", _ptr(logits.contiguous()), _ptr(dev_params), _ptr(out), r, vocab)
+    slices = self.lib.sb_sample_slices(r, vocab)
+    scratch = self._new(r * (2 + 2 * slices), dtype=torch.int32)
+    self._call("sb_sample", _ptr(logits.contiguous()), _ptr(dev_params), _ptr(out), r, vocab, _ptr(scratch))
+    self.launches += 2
     return out
 
   def decode_advance(self, sampled, token_ids, positions, q_start, sample_params, history, step_counter) -> None:
