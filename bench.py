@@ -125,15 +125,19 @@ def prefill_flops(cfg, layers, tokens):
 
 
 def reference_arm(args):
-  """The reference cannot run here: it needs JAX, which is not installed and cannot be
-  (no network); its attention kernel is a TPU Pallas kernel."""
-  why = "google-deepmind/simply needs jax, orbax and a TPU Pallas kernel; none can be installed offline here"
-  try:
-    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-    import jax  # noqa: F401
-    why = "jax is importable but the reference's paged attention is a TPU-only Pallas kernel"
-  except Exception:
-    pass
+  """Runs nothing: the reference installs only without its dependencies and cannot be imported
+  (`pip install --no-deps --target baseline/_ref` works; `import simply.model_lib` needs jax,
+  orbax and etils, which are not installed and cannot be, and its paged attention is a TPU
+  Pallas kernel)."""
+  why = "baseline/_ref is absent: google-deepmind/simply was not installed"
+  ref = os.path.join(ROOT, "baseline", "_ref")
+  if os.path.isdir(os.path.join(ref, "simply")):
+    sys.path.insert(0, ref)
+    try:
+      import simply.model_lib  # noqa: F401
+      why = "simply imports, but its paged attention is a TPU-only Pallas kernel with no CUDA path"
+    except Exception as e:  # ModuleNotFoundError: jax
+      why = f"import simply.model_lib fails offline: {type(e).__name__}: {e}"
   print(json.dumps({"impl": "reference", "unavailable": why}))
   return 0
 
