@@ -85,6 +85,11 @@ class DecoderModel:
             if hasattr(have, f))
         if not same:
           raise ValueError(f"layer {call.layer!r} cannot read cache {cache!r}: {need} vs {have}")
+        kept, wanted = getattr(have, "window", None), getattr(need, "window", None)
+        if kept is not None and (wanted is None or wanted > kept):
+          raise ValueError(
+              f"layer {call.layer!r} wants to see {wanted or 'all'} keys of cache {cache!r}, "
+              f"which keeps only a window of {kept}")
     return needs
 
   # ---- forward --------------------------------------------------------------

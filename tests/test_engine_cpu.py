@@ -1,0 +1,107 @@
+"""The engine's host side on a machine without a GPU: the cache manager, the step function,
+the scheduler and replay run with the plain-PyTorch kernel table (tests/reference_ops.py)
+and must reproduce the plain NumPy model under every way of cutting the work."""
+
+import numpy as np
+import pytest
+import torch
+
+from simply_b200 import Engine, EngineConfig, SamplingParams, StepEntry
+from simply_b200.engine.replay import engine_for_replay
+from tests import replay_cases as cases
+from tests import trace_util
+from tests.plain.gemma2_plain import PlainGemma2
+from tests.reference_ops import ReferenceOps
+from tests.tiny_models import write_tiny
+from tests.tolerances import assert_logits_close
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+  root = tmp_path_factory.mktemp("models")
+  out = {}
+  for which in ("a", "b"):
+    folder = write_tiny(which, root, "bfloat16")
+    plain = PlainGemma2(folder)
+    requests = cases.make_requests(which, plain.cfg["vocab_size"])
+    out[which] = (folder, plain, requests, {rid: plain.forward(t) for rid, t in requests.items()})
+  return out
+
+
+def cpu_engine(folder, dtype="float32", **kw):
+  kw.setdefault("page_size", 8)
+  kw.setdefault("batch_size", 4)
+  kw.setdefault("max_seq_len", 256)
+  return Engine.from_folder(folder, EngineConfig(activation_dtype=dtype, **kw),
+                            ops=ReferenceOps(getattr(torch, dtype)))
+
+
+@pytest.mark.parametrize("dtype,page", [("float32", 64), ("float32", 4), ("bfloat16", 8)])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_replay_four_ways(models, tmp_path, which, dtype, page):
+  folder, plain, requests, expected = models[which]
+  steps = cases.combined_trace(requests)
+  eng = engine_for_replay(folder, dtype, trace_util.tokens_needed(steps, page), page, poison_freed_pages=True,
+                          ops=ReferenceOps(getattr(torch, dtype)))
+  trace_util.run_in_process(eng, steps, str(tmp_path))
+  eng.cache.check_invariants()
+  assert eng.cache.min_free_pages() == eng.cache.num_pages  # every request was ended
+  cases.compare(trace_util.collect(steps, str(tmp_path), plain.cfg["vocab_size"]), requests, expected, dtype)
+
+
+def test_step_returns_only_wanted_rows_in_order(models):
+  folder, plain, requests, expected = models["a"]
+  eng = cpu_engine(folder)
+  (r0, t0), (r1, t1) = list(requests.items())[:2]
+  a, b = eng.open_request("a"), eng.open_request("b")
+  assert eng.step_raw([StepEntry(a, t0[:10], ()), StepEntry(b, t1[:4], ())]) is None
+  got = eng.step_raw([StepEntry(b, t1[4:9], (4, 0)), StepEntry(a, t0[10:12], (1,))]).numpy()
+  want = np.stack([expected[r1][8], expected[r1][4], expected[r0][11]])
+  assert_logits_close(got, want, "float32")
+  with pytest.raises(ValueError, match="outside its"):
+    eng.step_raw([StepEntry(a, [1, 2], (2,))])
+  with pytest.raises(ValueError, match="vocabulary"):
+    eng.step_raw([StepEntry(a, [10 ** 6], ())])
+
+
+@pytest.mark.parametrize("which,lengths,steps,page", [("a", (5, 11, 17), 8, 4), ("b", (1, 23, 40), 12, 8)])
+def test_generation_equals_plain(models, which, lengths, steps, page):
+  folder, plain, _, _ = models[which]
+  rng = np.random.default_rng(1)
+  prompts = [rng.integers(0, plain.cfg["vocab_size"], n).tolist() for n in lengths]
+  eng = cpu_engine(folder, page_size=page, max_num_issue_tokens=7)
+  got = eng.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=steps, stop_token_ids=()))
+  assert [r.output_token_ids for r in got] == [plain.greedy(p, steps) for p in prompts]
+  got = eng.generate(prompts, SamplingParams(temperature=0.8, seed=3, max_decode_steps=steps, stop_token_ids=()))
+  assert [r.output_token_ids for r in got] == [plain.sample(p, steps, 0.8, 3) for p in prompts]
+  eng.cache.check_invariants()
+
+
+def test_eos_ends_a_request(models):
+  folder, plain, _, _ = models["a"]
+  prompt = [3, 1, 4, 1, 5]
+  first = plain.greedy(prompt, 3)
+  eng = cpu_engine(folder)
+  r = eng.generate([prompt], SamplingParams(temperature=0.0, max_decode_steps=9, stop_token_ids=(first[2],)))[0]
+  assert r.output_token_ids == first[:first.index(first[2]) + 1] and r.finish_reason == "eos" and not r.is_truncated
+
+
+def test_preemption_gives_the_same_tokens(models):
+  folder, plain, _, _ = models["b"]
+  rng = np.random.default_rng(9)
+  prompts = [rng.integers(0, 1000, n).tolist() for n in (20, 25, 30)]
+  sp = SamplingParams(temperature=0.9, seed=2, max_decode_steps=30, stop_token_ids=())
+  roomy = cpu_engine(folder).generate(prompts, sp)
+  tight_engine = cpu_engine(folder, max_cache_tokens=120)
+  tight = tight_engine.generate(prompts, sp)
+  assert [r.output_token_ids for r in tight] == [r.output_token_ids for r in roomy]
+  assert sum(r.num_preemptions for r in tight) > 0
+  assert tight_engine.cache.min_free_pages() == tight_engine.cache.num_pages
+
+
+def test_the_package_has_no_cpu_path():
+  if torch.cuda.is_available():
+    pytest.skip("this machine has a GPU")
+  from simply_b200.kernels.ops import CudaOps, KernelError
+  with pytest.raises(KernelError, match="no CPU path"):
+    CudaOps(torch.bfloat16)

@@ -100,3 +100,13 @@ def test_sampling_masks():
   freq = np.bincount(draws, minlength=5) / 3000
   assert np.abs(freq - np.exp(logits)).max() < 0.03
   assert set(plain.sample_token(logits, 1.0, 2, 1.0, s, 4) for s in range(200)) == {0, 1}
+
+
+def test_plain_model_matches_its_committed_outputs():
+  """tests/golden/plain_tiny.npz was written by tests/golden/make_golden.py (float64)."""
+  import os
+  from tests.golden.make_golden import compute
+  path = os.path.join(os.path.dirname(__file__), "golden", "plain_tiny.npz")
+  golden = np.load(path)
+  for which, logits in compute().items():
+    np.testing.assert_allclose(logits, golden[which], atol=1e-6)
