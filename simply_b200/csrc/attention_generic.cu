@@ -48,6 +48,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
                                T* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
                                int head_dim, int page_size, int num_pages, float cap, int window,
                                int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];  // per warp: head_dim floats of q
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long item = (long long)blockIdx.x * GEN_WARPS + warp;
@@ -141,13 +143,13 @@ extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* 
   const unsigned blocks = (unsigned)((items + GEN_WARPS - 1) / GEN_WARPS);
   const size_t smem = (size_t)GEN_WARPS * head_dim * sizeof(float);
   if (dtype == SB_DTYPE_F32)
-    paged_attention_generic_kernel<float><<<blocks, GEN_WARPS * 32, smem, stream>>>(
-        (const float*)q, (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out,
-        num_tokens, num_q_heads, num_kv_heads, head_dim, page_size, num_pages, cap, window, err);
+    sb_launch(paged_attention_generic_kernel<float>, blocks, GEN_WARPS * 32, smem, stream, (const float*)q,
+        (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out, num_tokens,
+        num_q_heads, num_kv_heads, head_dim, page_size, num_pages, cap, window, err);
   else
-    paged_attention_generic_kernel<bf16><<<blocks, GEN_WARPS * 32, smem, stream>>>(
-        (const bf16*)q, (const bf16*)cache, block_table, max_pages, token_seq, positions, (bf16*)out,
-        num_tokens, num_q_heads, num_kv_heads, head_dim, page_size, num_pages, cap, window, err);
+    sb_launch(paged_attention_generic_kernel<bf16>, blocks, GEN_WARPS * 32, smem, stream, (const bf16*)q,
+        (const bf16*)cache, block_table, max_pages, token_seq, positions, (bf16*)out, num_tokens,
+        num_q_heads, num_kv_heads, head_dim, page_size, num_pages, cap, window, err);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -231,6 +231,8 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
 // Prefill: grid (items, kv heads), 128 threads.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [64][PITCH]
   bf16* sk = sq + 64 * PITCH;                    // [2][BN][PITCH]
@@ -316,6 +318,8 @@ constexpr int DEC_NT = DEC_WARPS * 32;
 constexpr int DEC_STAGES = 3;
 
 __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p, int* work_counter, int total_work) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [16][PITCH]
   bf16* sk = sq + 16 * PITCH;                    // [STAGES][DEC_BN][PITCH]
@@ -432,6 +436,329 @@ __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p,
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Decode with at most 8 query rows per (sequence, kv head): the usual case of one new token
+// and a group of up to 8 query heads.  Same persistent grid and chunks as above, but
+//  * the product is turned round: scores^T[16 keys x 8 rows] = K . Q^T, so the 16-row operand
+//    of the mma is a tile of keys and the 8-column operand is the queries, which stay in
+//    registers for a whole chunk; out^T[16 dims x 8 rows] += V^T . P^T likewise.  Half the
+//    tensor work, half the accumulator registers, no padding of 2 rows to 16;
+//  * P^T becomes the 8-column operand by transposing its 8x8 blocks across the warp
+//    (movmatrix), with no trip through shared memory;
+//  * key/value rows come in with one bulk copy per row (cp.async.bulk, completion counted
+//    on an mbarrier per stage) instead of 16-byte copies per thread.
+// Every wait on an mbarrier is bounded; on a time-out the block sets SB_ERR_TIMEOUT and leaves.
+// ---------------------------------------------------------------------------------------
+#define SB_ERR_TIMEOUT 8
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity; false after about a second without success.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (spin > 64) __nanosleep(200);
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy_row(void* dst, const void* src, int bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+
+constexpr int D8_BN = DH > 128 ? 32 : 64;  // keys per tile
+constexpr int D8_WARPS = D8_BN / 16;
+constexpr int D8_NT = D8_WARPS * 32;
+constexpr int D8_STAGES = 3;
+constexpr int ROW_BYTES = DH * (int)sizeof(bf16);
+#ifndef SB_D8_BULK
+#define SB_D8_BULK 0  // 1: one bulk copy per row (measured slower: 512-byte copies are too small)
+#endif
+
+__global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sk = reinterpret_cast<bf16*>(smem_raw);  // [STAGES][D8_BN][PITCH]
+  bf16* sv = sk + D8_STAGES * D8_BN * PITCH;     // [STAGES][D8_BN][PITCH]
+  __shared__ __align__(8) uint64_t full[D8_STAGES];
+  __shared__ long long row_src[D8_STAGES][D8_BN];
+  __shared__ int s_work;
+  __shared__ int s_failed;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int group = p.num_q_heads / p.num_kv_heads;
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < D8_STAGES; ++st) mbar_init(&full[st], D8_BN);
+    s_failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  unsigned tile_seq = 0;  // tiles this block has consumed so far: stage = seq % STAGES, parity from seq / STAGES
+  const size_t head_stride = (size_t)p.page_size * DH;
+  const size_t v_offset = (size_t)p.num_kv_heads * head_stride;
+
+  for (;;) {
+    if (threadIdx.x == 0) s_work = atomicAdd(work_counter, 1);
+    __syncthreads();
+    const int work = s_work;
+    const bool failed = s_failed != 0;
+    __syncthreads();  // everyone has read s_work; shared memory of the last item is free
+    if (work >= total_work || failed) break;
+    const int item = work / p.num_kv_heads, m = work - item * p.num_kv_heads;
+    const int b = p.items[2 * item], chunk_index = p.items[2 * item + 1];
+    if (b < 0) continue;  // filler item of a fixed-size work list
+    const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
+    const int rows_valid = q_len * group;  // <= 8 by the host's routing
+    const int kv_lo = p.window > 0 ? max(qs - p.window + 1, 0) : 0;
+    const int kv_hi = qs + q_len;
+    const int begin = max(chunk_index * p.chunk, (kv_lo / 64) * 64);
+    const int end = min((chunk_index + 1) * p.chunk, kv_hi);
+    const int n_tiles = end > begin ? (end - begin + D8_BN - 1) / D8_BN : 0;
+
+#if !SB_D8_BULK
+    // 16-byte copies per thread, as in the other kernels (one commit group per tile).
+    auto issue_tile = [&](int tile_index, unsigned seq) {
+      const int stage = seq % D8_STAGES;
+      load_kv_tile<D8_BN, D8_NT>(p, sk + (size_t)stage * D8_BN * PITCH, sv + (size_t)stage * D8_BN * PITCH,
+                                 row_src[stage], begin + tile_index * D8_BN, kv_lo, end, b, m);
+    };
+#else
+    // Thread i < D8_BN brings row i of a tile: both of its rows with one bulk copy each.
+    auto issue_tile = [&](int tile_index, unsigned seq) {
+      if (threadIdx.x >= D8_BN) return;
+      const int stage = seq % D8_STAGES;
+      const int j = begin + tile_index * D8_BN + threadIdx.x;
+      bf16* krow = sk + ((size_t)stage * D8_BN + threadIdx.x) * PITCH;
+      bf16* vrow = sv + ((size_t)stage * D8_BN + threadIdx.x) * PITCH;
+      long long src = -1;
+      if (j >= kv_lo && j < end) {
+        const int page_index = j / p.page_size;
+        const long long page = p.block_table[(size_t)b * p.max_pages + page_index];
+        if (page < 0 || page >= p.num_pages)
+          atomicOr(p.err, SB_ERR_BAD_PAGE);
+        else
+          src = (long long)(((size_t)page * 2 * p.num_kv_heads + m) * head_stride +
+                            (size_t)(j - page_index * p.page_size) * DH);
+      }
+      if (src >= 0) {
+        mbar_arrive_expect_tx(&full[stage], 2 * ROW_BYTES);
+        bulk_copy_row(krow, p.cache + src, ROW_BYTES, &full[stage]);
+        bulk_copy_row(vrow, p.cache + src + v_offset, ROW_BYTES, &full[stage]);
+      } else {
+        // Not a key of this request: its value row must read as zeros (0 * garbage could be NaN);
+        // its key row is masked by position whatever it holds.
+        for (int c = 0; c < CPR; ++c) *reinterpret_cast<uint4*>(vrow + c * 8) = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < CPR; ++c) *reinterpret_cast<uint4*>(krow + c * 8) = make_uint4(0, 0, 0, 0);
+        mbar_arrive(&full[stage]);
+      }
+    };
+#endif
+
+#if SB_D8_BULK
+    for (int st = 0; st < D8_STAGES - 1 && st < n_tiles; ++st) issue_tile(st, tile_seq + st);
+#else
+    for (int st = 0; st < D8_STAGES - 1; ++st) {
+      if (st < n_tiles) issue_tile(st, tile_seq + st);
+      cp_async_commit();
+    }
+#endif
+
+    // Queries: the 8-column operand, in registers for the whole chunk.  Column g is query row g.
+    uint32_t qf[DH / 16][2];
+    {
+      const bool valid = g < rows_valid;
+      const bf16* qrow = p.q + ((size_t)(row0 + (valid ? g / group : 0)) * p.num_q_heads + m * group +
+                                (valid ? g % group : 0)) * DH;
+#pragma unroll
+      for (int ks = 0; ks < DH / 16; ++ks) {
+        qf[ks][0] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+        qf[ks][1] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+      }
+    }
+    // This thread's two query rows are 2t and 2t + 1.
+    const int pos0 = 2 * t < rows_valid ? qs + (2 * t) / group : -1;
+    const int pos1 = 2 * t + 1 < rows_valid ? qs + (2 * t + 1) / group : -1;
+    const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[DH / 16][4];  // out^T: [dims 16 blk + g | g + 8][rows 2t | 2t + 1]
+#pragma unroll
+    for (int d = 0; d < DH / 16; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      const unsigned seq = tile_seq + it;
+      const int stage = seq % D8_STAGES;
+#if SB_D8_BULK
+      if (it + D8_STAGES - 1 < n_tiles) issue_tile(it + D8_STAGES - 1, seq + D8_STAGES - 1);
+      // A thread whose wait ran out skips the arithmetic; the block agrees on leaving at the barrier below.
+      const bool landed = mbar_wait_bounded(&full[stage], (seq / D8_STAGES) & 1);
+#else
+      cp_async_wait<D8_STAGES - 2>();
+      __syncthreads();  // tile `it` has landed for every thread; the stage of tile it - 1 is free
+      if (it + D8_STAGES - 1 < n_tiles) issue_tile(it + D8_STAGES - 1, seq + D8_STAGES - 1);
+      cp_async_commit();
+      const bool landed = true;
+#endif
+      if (landed) {
+      const bf16* kt = sk + ((size_t)stage * D8_BN + warp * 16) * PITCH;
+      const bf16* vt = sv + ((size_t)stage * D8_BN + warp * 16) * PITCH;
+      // scores^T for this warp's 16 keys; two accumulators so that the chain of mma's is half as long
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < DH / 16; ks += 2) {
+        uint32_t a[4], a2[4];
+        ldmatrix_x4(a, kt + (lane & 15) * PITCH + ks * 16 + (lane >> 4) * 8);
+        mma16816(s0, a, qf[ks][0], qf[ks][1]);
+        if (ks + 1 < DH / 16) {
+          ldmatrix_x4(a2, kt + (lane & 15) * PITCH + (ks + 1) * 16 + (lane >> 4) * 8);
+          mma16816(s1, a2, qf[ks + 1][0], qf[ks + 1][1]);
+        }
+      }
+      // s[0]: (key g, row 2t)  s[1]: (key g, row 2t+1)  s[2]: (key g+8, row 2t)  s[3]: (key g+8, row 2t+1)
+      const int j_lo = begin + it * D8_BN + warp * 16 + g;
+      float sc[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s0[e] + s1[e];
+        if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
+        const int j = j_lo + (e >> 1) * 8;
+        const int pos = (e & 1) ? pos1 : pos0;
+        const bool keep = j <= pos && (p.window <= 0 || pos - j < p.window);
+        sc[e] = keep ? v * LOG2E : -INFINITY;
+      }
+      float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float new0 = fmaxf(m0, mx0), new1 = fmaxf(m1, mx1);
+      const float use0 = new0 == -INFINITY ? 0.f : new0, use1 = new1 == -INFINITY ? 0.f : new1;
+      const float alpha0 = fast_exp2(m0 - use0), alpha1 = fast_exp2(m1 - use1);
+      m0 = new0;
+      m1 = new1;
+      const float p0 = fast_exp2(sc[0] - use0), p1 = fast_exp2(sc[1] - use1);
+      const float p2 = fast_exp2(sc[2] - use0), p3 = fast_exp2(sc[3] - use1);
+      l0 = l0 * alpha0 + p0 + p2;  // this thread's keys only; the eight g-lanes are added at the end
+      l1 = l1 * alpha1 + p1 + p3;
+      if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+#pragma unroll
+        for (int d = 0; d < DH / 16; ++d) {
+          o[d][0] *= alpha0;
+          o[d][1] *= alpha1;
+          o[d][2] *= alpha0;
+          o[d][3] *= alpha1;
+        }
+      }
+      // P^T as the 8-column operand: (keys 2t, 2t+1 | 2t+8, 2t+9 ; row g) from (key g | g+8 ; rows 2t, 2t+1).
+      const uint32_t b0 = movmatrix_trans(pack_bf16(p0, p1));
+      const uint32_t b1 = movmatrix_trans(pack_bf16(p2, p3));
+#pragma unroll
+      for (int d = 0; d < DH / 16; ++d) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, vt + (((lane >> 4) & 1) * 8 + (lane & 7)) * PITCH + d * 16 + ((lane >> 3) & 1) * 8);
+        mma16816(o[d], a, b0, b1);
+      }
+      }
+#if SB_D8_BULK
+      // Everyone is done with this stage before it is filled again; and did everyone get its tile?
+      if (!__syncthreads_and(landed ? 1 : 0)) {
+        ok = false;
+        break;
+      }
+#endif
+    }
+#if !SB_D8_BULK
+    cp_async_wait<0>();
+#endif
+    if (!ok) {
+      atomicOr(p.err, SB_ERR_TIMEOUT);
+      s_failed = 1;
+    }
+    tile_seq += n_tiles;
+    __syncthreads();
+    if (s_failed) {
+      // Copies of this block may still be in flight: give them a bounded time to land, then leave.
+      for (int st = 0; st < D8_STAGES; ++st) mbar_wait_bounded(&full[st], 0);
+      break;
+    }
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    // Merge the warps through shared memory (the tiles are no longer needed).
+    float* wm = reinterpret_cast<float*>(sk);  // [W][8] max, [W][8] sum, then [W][rows_valid][DH]
+    float* wl = wm + D8_WARPS * 8;
+    float* wo = wl + D8_WARPS * 8;
+    if (g == 0) {
+      wm[warp * 8 + 2 * t] = m0;
+      wm[warp * 8 + 2 * t + 1] = m1;
+      wl[warp * 8 + 2 * t] = l0;
+      wl[warp * 8 + 2 * t + 1] = l1;
+    }
+#pragma unroll
+    for (int d = 0; d < DH / 16; ++d) {
+      if (2 * t < rows_valid) {
+        wo[((size_t)warp * rows_valid + 2 * t) * DH + d * 16 + g] = o[d][0];
+        wo[((size_t)warp * rows_valid + 2 * t) * DH + d * 16 + g + 8] = o[d][2];
+      }
+      if (2 * t + 1 < rows_valid) {
+        wo[((size_t)warp * rows_valid + 2 * t + 1) * DH + d * 16 + g] = o[d][1];
+        wo[((size_t)warp * rows_valid + 2 * t + 1) * DH + d * 16 + g + 8] = o[d][3];
+      }
+    }
+    __syncthreads();
+    const size_t pidx = (size_t)item * p.num_kv_heads + m;
+    for (int i = threadIdx.x; i < rows_valid * DH; i += D8_NT) {
+      const int r = i / DH, d = i - r * DH;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < D8_WARPS; ++w) mx = fmaxf(mx, wm[w * 8 + r]);
+      float num = 0.f, den = 0.f;
+      if (mx != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < D8_WARPS; ++w) {
+          const float scale = fast_exp2(wm[w * 8 + r] - mx);
+          num += scale * wo[((size_t)w * rows_valid + r) * DH + d];
+          den += scale * wl[w * 8 + r];
+        }
+      }
+      p.part_o[(pidx * p.rows_max + r) * DH + d] = den > 0.f ? num / den : 0.f;
+      if (d == 0) {
+        p.part_ml[(pidx * p.rows_max + r) * 2] = mx;
+        p.part_ml[(pidx * p.rows_max + r) * 2 + 1] = den;
+      }
+    }
+    // The generic-proxy writes above must not be overtaken by the next item's bulk copies.
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+}
+
 // Merges the chunks of every (token, query head): one block each.  Its warps take the
 // chunks in turn (warp w: chunks w, w + 4, ...), then add up in a fixed order.
 constexpr int COMBINE_WARPS = 4;
@@ -441,7 +768,12 @@ __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     const int* __restrict__ token_seq, const int* __restrict__ cu_q,
                     const int* __restrict__ split_start, const int* __restrict__ split_count,
-                    bf16* __restrict__ out, int num_q_heads, int num_kv_heads, int rows_max) {
+                    bf16* __restrict__ out, int num_q_heads, int num_kv_heads, int rows_max,
+                    int* __restrict__ work_counter) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // The split-key kernel has finished: put its work counter back to zero for the next launch.
+  if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
   __shared__ float s_acc[COMBINE_WARPS][DH];
   __shared__ float s_den[COMBINE_WARPS];
   __shared__ float s_max[COMBINE_WARPS];
@@ -495,6 +827,9 @@ constexpr size_t DECODE_SMEM_KV = (size_t)(16 + 2 * DEC_STAGES * DEC_BN) * PITCH
 constexpr size_t DECODE_SMEM_MERGE =
     16 * PITCH * sizeof(bf16) + (size_t)(2 * DEC_WARPS * 16 + DEC_WARPS * 16 * DH) * sizeof(float);
 constexpr size_t DECODE_SMEM = DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE;
+constexpr size_t DECODE8_SMEM_KV = (size_t)(2 * D8_STAGES * D8_BN) * PITCH * sizeof(bf16);
+constexpr size_t DECODE8_SMEM_MERGE = (size_t)(2 * D8_WARPS * 8 + D8_WARPS * 8 * DH) * sizeof(float);
+constexpr size_t DECODE8_SMEM = DECODE8_SMEM_KV > DECODE8_SMEM_MERGE ? DECODE8_SMEM_KV : DECODE8_SMEM_MERGE;
 
 }  // namespace
 
@@ -521,7 +856,7 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attn_prefill_kernel<<<dim3(num_items, num_kv_heads), NT, PREFILL_SMEM, stream>>>(p);
+  sb_launch(attn_prefill_kernel, dim3(num_items, num_kv_heads), NT, PREFILL_SMEM, stream, p);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -529,15 +864,16 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
 // Split-key attention for sequences with at most 16 query rows per kv head, and the merge.
 // items: [num_items, 2] (sequence or -1, chunk index); chunk: keys per chunk, a multiple of 64;
 // part_o / part_ml: scratch of num_items * Hkv * rows_max * (DH | 2) floats;
-// work_counter: one int of scratch, zeroed here on the stream before the launch;
+// work_counter: one int that is zero before the first launch; the merge kernel zeroes it again;
 // split_start / split_count: per sequence, its range of items (count 0: not handled here).
 extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int* block_table, int max_pages,
                                      const int* cu_q, const int* q_start, const int* token_seq, void* out,
                                      int num_tokens, int num_q_heads, int num_kv_heads, int page_size,
                                      int num_pages, float cap, int window, const int* items, int num_items,
                                      int chunk, float* part_o, float* part_ml, int* work_counter,
-                                     int rows_max, const int* split_start, const int* split_count, int* err,
-                                     cudaStream_t stream) {
+                                     int rows_max, const int* split_start, const int* split_count, int variant,
+                                     int* err, cudaStream_t stream) {
+  // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel); 16 forces the 16-row kernel.
   if (num_items == 0) return 0;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || rows_max > 16 || chunk % 64) return -8;
   AttnParams p{};
@@ -558,15 +894,30 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
     if (e != cudaSuccess) return (int)e;
     resident = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
   }
+  static int resident8 = 0;
+  if (resident8 == 0) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)DECODE8_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    int per_sm = 0, sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode8_kernel, D8_NT, DECODE8_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    resident8 = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
+  }
   const int total_work = num_items * num_kv_heads;
-  cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(int), stream);
-  if (e != cudaSuccess) return (int)e;
-  attn_decode_kernel<<<total_work < resident ? total_work : resident, DEC_NT, DECODE_SMEM, stream>>>(
-      p, work_counter, total_work);
+  if (rows_max <= 8 && variant != 16) {
+    sb_launch(attn_decode8_kernel, total_work < resident8 ? total_work : resident8, D8_NT, DECODE8_SMEM, stream,
+        p, work_counter, total_work);
+  } else {
+    sb_launch(attn_decode_kernel, total_work < resident ? total_work : resident, DEC_NT, DECODE_SMEM, stream,
+        p, work_counter, total_work);
+  }
   SB_LAUNCH_CHECK();
-  attn_combine_kernel<<<(unsigned)(num_tokens * num_q_heads), COMBINE_WARPS * 32, 0, stream>>>(
+  sb_launch(attn_combine_kernel, (unsigned)(num_tokens * num_q_heads), COMBINE_WARPS * 32, 0, stream,
       part_o, part_ml, token_seq, cu_q, split_start, split_count, (bf16*)out, num_q_heads, num_kv_heads,
-      rows_max);
+      rows_max, work_counter);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -111,6 +111,43 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Programmatic dependent launch.  Every kernel of the engine begins with
+// `pdl_launch_dependents(); pdl_wait();` (or does work that depends on nothing written by
+// earlier kernels, such as fetching weights, between the two).  The first lets the next
+// kernel of the stream start as soon as all blocks of this one have started; the second
+// blocks until every earlier kernel has finished and its writes are visible.  Launched
+// without the attribute both are no-ops, so a kernel is always correct on its own.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <stdlib.h>
+
+// SIMPLY_B200_PDL=0 in the environment launches every kernel the plain way.
+inline bool sb_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("SIMPLY_B200_PDL");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = sb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 #define SB_LAUNCH_CHECK()                      \
   do {                                         \
     cudaError_t e__ = cudaGetLastError();      \

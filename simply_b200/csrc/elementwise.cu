@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float scale,
                              float* __restrict__ out, int width, int vocab, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -43,9 +45,11 @@ extern "C" int sb_embed(const void* table, int table_dtype, const int* ids, floa
                         int num_tokens, int width, int vocab, int* err, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (table_dtype == SB_DTYPE_F32)
-    embed_kernel<float><<<num_tokens, 256, 0, stream>>>((const float*)table, ids, scale, out, width, vocab, err);
+    sb_launch(embed_kernel<float>, num_tokens, 256, 0, stream, (const float*)table, ids, scale, out, width,
+        vocab, err);
   else
-    embed_kernel<bf16><<<num_tokens, 256, 0, stream>>>((const bf16*)table, ids, scale, out, width, vocab, err);
+    sb_launch(embed_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)table, ids, scale, out, width,
+        vocab, err);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -64,6 +68,8 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
                                      int post_plus_one, const void* __restrict__ w_pre, int pre_f32,
                                      float eps_pre, int pre_plus_one, const int* __restrict__ rows,
                                      T* __restrict__ y, int width, int num_rows_total, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row[];  // width floats + 33 scratch
   float* scratch = row + width;
   const int r = blockIdx.x;
@@ -170,15 +176,13 @@ extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const v
   if (dtype == SB_DTYPE_F32) {
     auto k = residual_norm_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<num_rows, threads, smem, stream>>>(h, (const float*)branch, w_post, post_f32, eps_post, post_plus_one,
-                                           w_pre, pre_f32, eps_pre, pre_plus_one, rows, (float*)y, width,
-                                           num_rows_total, err);
+    sb_launch(k, num_rows, threads, smem, stream, h, (const float*)branch, w_post, post_f32, eps_post,
+        post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (float*)y, width, num_rows_total, err);
   } else {
     auto k = residual_norm_kernel<bf16>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<num_rows, threads, smem, stream>>>(h, (const bf16*)branch, w_post, post_f32, eps_post, post_plus_one,
-                                           w_pre, pre_f32, eps_pre, pre_plus_one, rows, (bf16*)y, width,
-                                           num_rows_total, err);
+    sb_launch(k, num_rows, threads, smem, stream, h, (const bf16*)branch, w_post, post_f32, eps_post,
+        post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (bf16*)y, width, num_rows_total, err);
   }
   SB_LAUNCH_CHECK();
   return 0;
@@ -190,6 +194,8 @@ extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const v
 template <typename Tin, typename Tout>
 __global__ void rms_norm_kernel(const Tin* __restrict__ x, const void* __restrict__ w, int w_f32, float eps,
                                 int plus_one, Tout* __restrict__ y, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row[];
   float* scratch = row + width;
   const Tin* xp = x + (size_t)blockIdx.x * width;
@@ -213,7 +219,7 @@ static int launch_rms_norm(const void* x, const void* w, int w_f32, float eps, i
   if (smem > 200 * 1024) return -2;
   auto k = rms_norm_kernel<Tin, Tout>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  k<<<num_rows, 256, smem, stream>>>((const Tin*)x, w, w_f32, eps, plus_one, (Tout*)y, width);
+  sb_launch(k, num_rows, 256, smem, stream, (const Tin*)x, w, w_f32, eps, plus_one, (Tout*)y, width);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -234,6 +240,8 @@ extern "C" int sb_rms_norm(const void* x, int in_dtype, const void* w, int w_f32
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out,
                                    int width, int num_rows_total, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   int src = rows[blockIdx.x];
   if (src < 0 || src >= num_rows_total) {
     if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_ROW);
@@ -247,15 +255,19 @@ extern "C" int sb_gather_rows(const void* x, int dtype, const int* rows, void* o
                               int num_rows_total, int* err, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   if (dtype == SB_DTYPE_F32)
-    gather_rows_kernel<float><<<num_rows, 256, 0, stream>>>((const float*)x, rows, (float*)out, width, num_rows_total, err);
+    sb_launch(gather_rows_kernel<float>, num_rows, 256, 0, stream, (const float*)x, rows, (float*)out,
+        width, num_rows_total, err);
   else
-    gather_rows_kernel<bf16><<<num_rows, 256, 0, stream>>>((const bf16*)x, rows, (bf16*)out, width, num_rows_total, err);
+    sb_launch(gather_rows_kernel<bf16>, num_rows, 256, 0, stream, (const bf16*)x, rows, (bf16*)out, width,
+        num_rows_total, err);
   SB_LAUNCH_CHECK();
   return 0;
 }
 
 template <typename T>
 __global__ void add_to_residual_kernel(float* __restrict__ h, const T* __restrict__ x, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) h[i] += to_f32<T>(x[i]);
 }
@@ -264,15 +276,17 @@ extern "C" int sb_add_to_residual(float* h, const void* x, int dtype, long long 
   if (n == 0) return 0;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == SB_DTYPE_F32)
-    add_to_residual_kernel<float><<<blocks, 256, 0, stream>>>(h, (const float*)x, (size_t)n);
+    sb_launch(add_to_residual_kernel<float>, blocks, 256, 0, stream, h, (const float*)x, (size_t)n);
   else
-    add_to_residual_kernel<bf16><<<blocks, 256, 0, stream>>>(h, (const bf16*)x, (size_t)n);
+    sb_launch(add_to_residual_kernel<bf16>, blocks, 256, 0, stream, h, (const bf16*)x, (size_t)n);
   SB_LAUNCH_CHECK();
   return 0;
 }
 
 template <typename Tin, typename Tout>
 __global__ void cast_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = from_f32<Tout>(to_f32<Tin>(x[i]));
 }
@@ -281,9 +295,9 @@ extern "C" int sb_cast(const void* x, int in_dtype, void* y, int out_dtype, long
   if (n == 0) return 0;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (in_dtype == SB_DTYPE_F32 && out_dtype == SB_DTYPE_BF16)
-    cast_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)x, (bf16*)y, (size_t)n);
+    sb_launch(cast_kernel<float, bf16>, blocks, 256, 0, stream, (const float*)x, (bf16*)y, (size_t)n);
   else if (in_dtype == SB_DTYPE_BF16 && out_dtype == SB_DTYPE_F32)
-    cast_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)x, (float*)y, (size_t)n);
+    sb_launch(cast_kernel<bf16, float>, blocks, 256, 0, stream, (const bf16*)x, (float*)y, (size_t)n);
   else
     return -3;
   SB_LAUNCH_CHECK();
@@ -297,6 +311,8 @@ extern "C" int sb_cast(const void* x, int in_dtype, void* y, int out_dtype, long
 __global__ void rotation_tables_kernel(const int* __restrict__ positions, const float* __restrict__ timescale,
                                        float scale_factor, float* __restrict__ cos_out,
                                        float* __restrict__ sin_out, int num_tokens, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= num_tokens * half) return;
   const int t = i / half, j = i - t * half;
@@ -312,8 +328,8 @@ extern "C" int sb_rotation_tables(const int* positions, const float* timescale, 
                                   cudaStream_t stream) {
   const int n = num_tokens * half;
   if (n == 0) return 0;
-  rotation_tables_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, timescale, scale_factor, cos_out,
-                                                              sin_out, num_tokens, half);
+  sb_launch(rotation_tables_kernel, (n + 255) / 256, 256, 0, stream, positions, timescale, scale_factor,
+      cos_out, sin_out, num_tokens, half);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -333,6 +349,8 @@ __global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const float* 
                                         int max_pages, const int* __restrict__ token_seq,
                                         const int* __restrict__ positions, int num_q_heads, int num_kv_proj,
                                         int head_dim, int page_size, int num_pages, int write_cache, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = head_dim / 2;
   const int heads = num_q_heads + 2 * num_kv_proj;
@@ -422,13 +440,13 @@ extern "C" int sb_rope_cache_write(const void* qkv, int dtype, const float* cos_
   if (num_tokens == 0) return 0;
   if (head_dim % 2) return -4;
   if (dtype == SB_DTYPE_F32)
-    rope_cache_write_kernel<float><<<num_tokens, 256, 0, stream>>>(
-        (const float*)qkv, cos_t, sin_t, q_scale, (float*)q_out, (float*)cache, block_table, max_pages,
-        token_seq, positions, num_q_heads, num_kv_proj, head_dim, page_size, num_pages, write_cache, err);
+    sb_launch(rope_cache_write_kernel<float>, num_tokens, 256, 0, stream, (const float*)qkv, cos_t, sin_t,
+        q_scale, (float*)q_out, (float*)cache, block_table, max_pages, token_seq, positions, num_q_heads,
+        num_kv_proj, head_dim, page_size, num_pages, write_cache, err);
   else
-    rope_cache_write_kernel<bf16><<<num_tokens, 256, 0, stream>>>(
-        (const bf16*)qkv, cos_t, sin_t, q_scale, (bf16*)q_out, (bf16*)cache, block_table, max_pages,
-        token_seq, positions, num_q_heads, num_kv_proj, head_dim, page_size, num_pages, write_cache, err);
+    sb_launch(rope_cache_write_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)qkv, cos_t, sin_t,
+        q_scale, (bf16*)q_out, (bf16*)cache, block_table, max_pages, token_seq, positions, num_q_heads,
+        num_kv_proj, head_dim, page_size, num_pages, write_cache, err);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -449,6 +467,8 @@ __device__ __forceinline__ float apply_activation(float g, int act) {
 template <typename T>
 __global__ void gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden,
                                             int act, size_t chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int N = Vec<T>::N;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= chunks) return;
@@ -465,6 +485,8 @@ __global__ void gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden, int act,
                                         size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const size_t t = i / hidden, f = i - t * hidden;
@@ -481,16 +503,18 @@ extern "C" int sb_gated_activation(const void* gate_up, int dtype, void* z, int 
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == SB_DTYPE_F32) {
     if (hidden % 4 == 0)
-      gated_activation_vec_kernel<float><<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(
-          (const float*)gate_up, (float*)z, hidden, act, n / 4);
+      sb_launch(gated_activation_vec_kernel<float>, (unsigned)((n / 4 + 255) / 256), 256, 0, stream, (const
+          float*)gate_up, (float*)z, hidden, act, n / 4);
     else
-      gated_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)z, hidden, act, n);
+      sb_launch(gated_activation_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)z,
+          hidden, act, n);
   } else {
     if (hidden % 8 == 0)
-      gated_activation_vec_kernel<bf16><<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(
-          (const bf16*)gate_up, (bf16*)z, hidden, act, n / 8);
+      sb_launch(gated_activation_vec_kernel<bf16>, (unsigned)((n / 8 + 255) / 256), 256, 0, stream, (const
+          bf16*)gate_up, (bf16*)z, hidden, act, n / 8);
     else
-      gated_activation_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)z, hidden, act, n);
+      sb_launch(gated_activation_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)z,
+          hidden, act, n);
   }
   SB_LAUNCH_CHECK();
   return 0;
@@ -500,13 +524,15 @@ extern "C" int sb_gated_activation(const void* gate_up, int dtype, void* z, int 
 // Soft cap in place on float32 logits: x = cap * tanh(x / cap).  simply/model_lib.py:107-109.
 // ---------------------------------------------------------------------------
 __global__ void soft_cap_kernel(float* __restrict__ x, float cap, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
 extern "C" int sb_soft_cap(float* x, float cap, long long n, cudaStream_t stream) {
   if (n == 0 || cap <= 0.f) return 0;
-  soft_cap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, cap, (size_t)n);
+  sb_launch(soft_cap_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, cap, (size_t)n);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -522,6 +548,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       int* __restrict__ positions, int* __restrict__ q_start,
                                       int* __restrict__ sample_params, int* __restrict__ history,
                                       int* __restrict__ step_counter, int batch) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *step_counter;
   if (i < batch) {
@@ -540,8 +568,8 @@ extern "C" int sb_decode_advance(const int* sampled, int* token_ids, int* positi
                                  int* sample_params, int* history, int* step_counter, int batch,
                                  cudaStream_t stream) {
   if (batch <= 0 || batch > 1024) return -10;  // one block of 1024 threads covers the batch
-  decode_advance_kernel<<<1, 1024, 0, stream>>>(sampled, token_ids, positions, q_start, sample_params, history,
-                                                step_counter, batch);
+  sb_launch(decode_advance_kernel, 1, 1024, 0, stream, sampled, token_ids, positions, q_start,
+      sample_params, history, step_counter, batch);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -14,6 +14,8 @@ __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restric
                                                           const float* __restrict__ w,
                                                           float* __restrict__ out, int M, int N, int K,
                                                           float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -64,7 +66,7 @@ extern "C" int sb_gemm_f32_nt(const float* x, const float* w, float* out, int M,
   if (M == 0 || N == 0) return 0;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return -6;
-  gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, out, M, N, K, cap);
+  sb_launch(gemm_f32_nt_kernel, grid, 256, 0, stream, x, w, out, M, N, K, cap);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -44,6 +44,7 @@ template <int MT, int WARPS, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void* __restrict__ out, int M,
                    int N, int K, float cap, int act) {
+  pdl_launch_dependents();
   constexpr int SETS = EPI == 2 ? 2 : 1;
   __shared__ float partial[WARPS][SETS][MT][16][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -74,22 +75,36 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
 
   const int steps = (K + 31) / 32;
   constexpr int UNROLL = SETS == 2 ? 2 : 4;
-  for (int s0 = warp; s0 < steps; s0 += WARPS * UNROLL) {
-    uint4 wa[UNROLL][SETS][2];
-    uint4 xv[UNROLL][MT];
+  constexpr int STRIDE = WARPS * UNROLL;
+  // Weights do not depend on earlier kernels: the first batch is fetched before the wait, so
+  // the stream of weights starts while the kernel before this one still runs.
+  uint4 wa[UNROLL][SETS][2];
+  auto load_weights = [&](uint4 (&dst)[UNROLL][SETS][2], int s0) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (s0 + u * WARPS) * 32 + t * 8;
       const bool ok = k < K;  // K is a multiple of 8, so a chunk is whole or absent
 #pragma unroll
       for (int s = 0; s < SETS; ++s) {
-        wa[u][s][0] = ok ? load_stream16(wr[s][0] + k) : make_uint4(0, 0, 0, 0);
-        wa[u][s][1] = ok ? load_stream16(wr[s][1] + k) : make_uint4(0, 0, 0, 0);
+        dst[u][s][0] = ok ? load_stream16(wr[s][0] + k) : make_uint4(0, 0, 0, 0);
+        dst[u][s][1] = ok ? load_stream16(wr[s][1] + k) : make_uint4(0, 0, 0, 0);
       }
+    }
+  };
+  load_weights(wa, warp);
+  pdl_wait();
+  for (int s0 = warp; s0 < steps; s0 += STRIDE) {
+    uint4 xv[UNROLL][MT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (s0 + u * WARPS) * 32 + t * 8;
+      const bool ok = k < K;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
         xv[u][mt] = (ok && xok[mt]) ? __ldg(reinterpret_cast<const uint4*>(xr[mt] + k)) : make_uint4(0, 0, 0, 0);
     }
+    uint4 wn[UNROLL][SETS][2];  // the next batch is in flight while this one is multiplied
+    if (s0 + STRIDE < steps) load_weights(wn, s0 + STRIDE);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
@@ -101,6 +116,15 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
           mma_bf16_16816(acc[s][mt], wa[u][s][0].z, wa[u][s][1].z, wa[u][s][0].w, wa[u][s][1].w, xv[u][mt].z,
                          xv[u][mt].w);
         }
+    if (s0 + STRIDE < steps) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+          wa[u][s][0] = wn[u][s][0];
+          wa[u][s][1] = wn[u][s][1];
+        }
+    }
   }
   // acc[..][0,1]: weight row g, tokens 2t, 2t+1; acc[..][2,3]: weight row g + 8.
 #pragma unroll
@@ -146,11 +170,14 @@ static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, 
   const int n_out = epilogue == 2 ? N / 2 : N;
   const unsigned blocks = (unsigned)((n_out + 15) / 16);
   if (epilogue == 0)
-    skinny_gemm_kernel<MT, WARPS, 0><<<blocks, WARPS * 32, 0, stream>>>(x, w, out, M, N, K, cap, act);
+    sb_launch(skinny_gemm_kernel<MT, WARPS, 0>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+        act);
   else if (epilogue == 1)
-    skinny_gemm_kernel<MT, WARPS, 1><<<blocks, WARPS * 32, 0, stream>>>(x, w, out, M, N, K, cap, act);
+    sb_launch(skinny_gemm_kernel<MT, WARPS, 1>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+        act);
   else
-    skinny_gemm_kernel<MT, WARPS, 2><<<blocks, WARPS * 32, 0, stream>>>(x, w, out, M, N, K, cap, act);
+    sb_launch(skinny_gemm_kernel<MT, WARPS, 2>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+        act);
   SB_LAUNCH_CHECK();
   return 0;
 }

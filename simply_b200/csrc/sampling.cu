@@ -107,6 +107,8 @@ __device__ float block_max(float v, float* scratch) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_threshold_kernel(const float* __restrict__ logits, const int* __restrict__ params,
                         uint32_t* __restrict__ thresholds, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float fscratch[33];
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * vocab;
@@ -169,6 +171,8 @@ __global__ void __launch_bounds__(SLICE_THREADS)
 sample_slice_kernel(const float* __restrict__ logits, const int* __restrict__ params,
                     const uint32_t* __restrict__ thresholds, ArgMax* __restrict__ partial, int vocab,
                     int slice_len) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ ArgMax ascratch[33];
   const int r = blockIdx.y, slice = blockIdx.x;
   const float* row = logits + (size_t)r * vocab;
@@ -200,6 +204,8 @@ sample_slice_kernel(const float* __restrict__ logits, const int* __restrict__ pa
 }
 
 __global__ void sample_final_kernel(const ArgMax* __restrict__ partial, int* __restrict__ out, int slices) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, lane = threadIdx.x;
   ArgMax best{-FLT_MAX, 0x7fffffff};
   for (int s = lane; s < slices; s += 32) best = better(best, partial[(size_t)r * slices + s]);
@@ -229,12 +235,13 @@ extern "C" int sb_sample(const float* logits, const int* params, int* out, int n
   const int slice_len = ((vocab + slices - 1) / slices + 3) / 4 * 4;
   uint32_t* thresholds = reinterpret_cast<uint32_t*>(scratch);
   ArgMax* partial = reinterpret_cast<ArgMax*>(thresholds + num_rows + (num_rows & 1));
-  sample_threshold_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, params, thresholds, vocab);
+  sb_launch(sample_threshold_kernel, num_rows, SAMPLE_THREADS, 0, stream, logits, params, thresholds,
+      vocab);
   SB_LAUNCH_CHECK();
-  sample_slice_kernel<<<dim3(slices, num_rows), SLICE_THREADS, 0, stream>>>(logits, params, thresholds, partial,
-                                                                          vocab, slice_len);
+  sb_launch(sample_slice_kernel, dim3(slices, num_rows), SLICE_THREADS, 0, stream, logits, params,
+      thresholds, partial, vocab, slice_len);
   SB_LAUNCH_CHECK();
-  sample_final_kernel<<<num_rows, 32, 0, stream>>>(partial, out, slices);
+  sb_launch(sample_final_kernel, num_rows, 32, 0, stream, partial, out, slices);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -28,6 +28,7 @@ _ERRORS = {
     1: "a block-table entry outside the page pool was about to be followed",
     2: "a token id outside the embedding table",
     4: "a gather row outside the batch",
+    8: "a wait for a bulk copy timed out",
 }
 _STATUS = {
     -2: "row too wide for the norm kernel's shared-memory buffer",
@@ -78,12 +79,16 @@ class CudaOps:
     self._declare()
     self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
     self._attn_fns: dict[int, tuple] = {}
+    # Work counter of the split-key attention kernel: zero between launches (its merge kernel resets it).
+    self._attn_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
     # bfloat16 attention runs on tensor cores where the shape allows; False forces the general kernel.
     self.tensor_core_attention = True
     # Split-key attention: about this many (sequence, chunk) items per kv head are aimed for;
     # decode_chunk > 0 fixes the chunk length instead (a multiple of 64).
     self.decode_target_items = 148 * 2
     self.decode_chunk = 0
+    # 0: the kernel is picked by the number of query rows; 16 forces the 16-row kernel (tests).
+    self.decode_variant = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
@@ -166,7 +171,7 @@ class CudaOps:
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
                          c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_int,
-                         c_void, c_void, c_void, c_void]
+                         c_void, c_void, c_int, c_void, c_void]
       decode.restype = c_int
       fns = self._attn_fns[head_dim] = (prefill, decode)
     return fns
@@ -420,11 +425,11 @@ class CudaOps:
         n = plan["num_decode"] * num_kv_heads * plan["rows_max"]
         part_o = self._new(n * head_dim, dtype=torch.float32)
         part_ml = self._new(n * 2, dtype=torch.float32)
-        counter = self._new(1, dtype=torch.int32)
         rc = decode(*common, _ptr(ctx.token_seq), _ptr(out), t, *sizes, _ptr(plan["decode_items"]),
-                    plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), _ptr(counter),
+                    plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), _ptr(self._attn_counter),
                     plan["rows_max"],
-                    _ptr(plan["split_start"]), _ptr(plan["split_count"]), _ptr(self.err), self._stream())
+                    _ptr(plan["split_start"]), _ptr(plan["split_count"]), self.decode_variant, _ptr(self.err),
+                    self._stream())
         self.launches += 2
         if rc:
           raise KernelError(f"sb_attn_decode: {_STATUS.get(rc, rc)}")

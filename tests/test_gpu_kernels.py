@@ -253,24 +253,30 @@ def test_paged_attention_general_kernel_bfloat16(general_bf16, hq, hkv, dh, ps, 
   close(got, run_attention(ref, q, sc, hq, hkv, dh, cap, window), torch.bfloat16, 2.0)
 
 
-@pytest.mark.parametrize("chunk", [64, 128, 0])
+@pytest.mark.parametrize("chunk,rows", [(64, 16), (128, 8), (0, 8), (256, 16), (64, 8)])
 @pytest.mark.parametrize("hq,hkv,dh,ps,window,cap", ATTN_CASES)
-def test_split_key_attention_chunks(table, chunk, hq, hkv, dh, ps, window, cap):
-  """Only short entries (the split-key kernel), long histories, several chunk lengths."""
+def test_split_key_attention_chunks(table, chunk, rows, hq, hkv, dh, ps, window, cap):
+  """Only short entries (the split-key kernels: up to 16 query rows per kv head, and the
+  turned-round one for up to 8), long histories, several chunk lengths."""
   ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
   group = hq // hkv
-  seqs = [(1000, 1), (0, 1), (63, 1), (64, 16 // group), (700, 2 if group <= 8 else 1), (129, 1)]
+  few = max(rows // group, 1)
+  seqs = [(1000, 1), (0, 1), (63, 1), (64, few), (700, min(2, few)), (129, 1), (31, 1), (255, 1)]
   sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=torch.bfloat16,
                      device="cuda", ops=ops, seed=6)
   q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 1.5).to(torch.bfloat16).cuda()
   ops.decode_chunk = chunk
+  want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)
   try:
-    got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+    for variant in (0, 16):
+      ops.decode_variant = variant
+      got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+      ops.check_errors()
+      assert torch.isfinite(got).all()
+      close(got, want, torch.bfloat16, 2.0)
   finally:
     ops.decode_chunk = 0
-  ops.check_errors()
-  assert torch.isfinite(got).all()
-  close(got, run_attention(ref, q, sc, hq, hkv, dh, cap, window), torch.bfloat16, 2.0)
+    ops.decode_variant = 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
