@@ -20,7 +20,9 @@
 //    output) that `combine` merges over chunks in a fixed order.
 // Keys and values come from the paged cache through the block table with 16-byte
 // cp.async copies; rows outside what the request holds are zero-filled, never read.
+#include <cuda.h>
 #include <float.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -445,8 +447,12 @@ __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p,
 //    tensor work, half the accumulator registers, no padding of 2 rows to 16;
 //  * P^T becomes the 8-column operand by transposing its 8x8 blocks across the warp
 //    (movmatrix), with no trip through shared memory;
-//  * key/value rows come in with one bulk copy per row (cp.async.bulk, completion counted
-//    on an mbarrier per stage) instead of 16-byte copies per thread.
+//  * with USE_TMA, key/value tiles come in through the tensor memory accelerator: one
+//    elected thread issues a few box copies per tile (`cp.async.bulk.tensor.2d`, 128-byte
+//    swizzle, completion counted on an mbarrier per stage) instead of two thousand 16-byte
+//    copies with their address arithmetic.  It needs a head size that is a multiple of 64 and
+//    a page size that is a power of two; otherwise the 16-byte copies are used.
+//    (One bulk copy per 512-byte row, without a tensor map, was measured slower than either.)
 // Every wait on an mbarrier is bounded; on a time-out the block sets SB_ERR_TIMEOUT and leaves.
 // ---------------------------------------------------------------------------------------
 #define SB_ERR_TIMEOUT 8
@@ -454,9 +460,6 @@ __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p,
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, int bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -478,11 +481,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
   }
   return false;
 }
-__device__ __forceinline__ void bulk_copy_row(void* dst, const void* src, int bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                   smem_u32(dst)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
+// One box of the tensor map (columns [col, col + 64), rows [row, row + box rows)) to shared memory.
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int col, int row, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(col), "r"(row), "r"(smem_u32(bar))
+      : "memory");
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   uint32_t y;
@@ -494,17 +499,31 @@ constexpr int D8_BN = DH > 128 ? 32 : 64;  // keys per tile
 constexpr int D8_WARPS = D8_BN / 16;
 constexpr int D8_NT = D8_WARPS * 32;
 constexpr int D8_STAGES = 3;
-constexpr int ROW_BYTES = DH * (int)sizeof(bf16);
-#ifndef SB_D8_BULK
-#define SB_D8_BULK 0  // 1: one bulk copy per row (measured slower: 512-byte copies are too small)
-#endif
+constexpr bool TMA_OK = DH % 64 == 0;        // 128-byte swizzled boxes of 64 columns
+constexpr int SLABS = TMA_OK ? DH / 64 : 1;  // 64-column slabs of a tile in the swizzled layout
+constexpr int SLAB_ELEMS = D8_BN * 64;       // elements of one slab of one tile
 
-__global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work) {
+// Element (row, dim) of a tile.  Swizzled layout: [slab][row][64 columns], the 16-byte chunks of
+// a 128-byte row XOR-ed with the row's low three bits (what the TMA's 128-byte swizzle writes).
+template <bool USE_TMA>
+__device__ __forceinline__ const bf16* tile_at(const bf16* tile, int row, int dim) {
+  if (USE_TMA) return tile + (dim >> 6) * SLAB_ELEMS + row * 64 + ((((dim & 63) >> 3) ^ (row & 7)) << 3) + (dim & 7);
+  return tile + row * PITCH + dim;
+}
+
+template <bool USE_TMA>
+__global__ void __launch_bounds__(D8_NT)
+attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work, const __grid_constant__ CUtensorMap tmap,
+                    int box_rows) {
   pdl_launch_dependents();
   pdl_wait();
+  constexpr int TILE_ELEMS = USE_TMA ? D8_BN * DH : D8_BN * PITCH;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* sk = reinterpret_cast<bf16*>(smem_raw);  // [STAGES][D8_BN][PITCH]
-  bf16* sv = sk + D8_STAGES * D8_BN * PITCH;     // [STAGES][D8_BN][PITCH]
+  // The swizzle pattern is a function of the address: tiles start on a 1024-byte boundary
+  // (the launch adds 1024 bytes of slack for this).
+  unsigned char* aligned = smem_raw + (USE_TMA ? ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u) : 0u);
+  bf16* sk = reinterpret_cast<bf16*>(aligned);  // [STAGES] key tiles
+  bf16* sv = sk + D8_STAGES * TILE_ELEMS;        // [STAGES] value tiles
   __shared__ __align__(8) uint64_t full[D8_STAGES];
   __shared__ long long row_src[D8_STAGES][D8_BN];
   __shared__ int s_work;
@@ -512,14 +531,12 @@ __global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p,
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int group = p.num_q_heads / p.num_kv_heads;
   if (threadIdx.x == 0) {
-    for (int st = 0; st < D8_STAGES; ++st) mbar_init(&full[st], D8_BN);
+    for (int st = 0; st < D8_STAGES; ++st) mbar_init(&full[st], 1);
     s_failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
   unsigned tile_seq = 0;  // tiles this block has consumed so far: stage = seq % STAGES, parity from seq / STAGES
-  const size_t head_stride = (size_t)p.page_size * DH;
-  const size_t v_offset = (size_t)p.num_kv_heads * head_stride;
 
   for (;;) {
     if (threadIdx.x == 0) s_work = atomicAdd(work_counter, 1);
@@ -539,53 +556,48 @@ __global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p,
     const int end = min((chunk_index + 1) * p.chunk, kv_hi);
     const int n_tiles = end > begin ? (end - begin + D8_BN - 1) / D8_BN : 0;
 
-#if !SB_D8_BULK
-    // 16-byte copies per thread, as in the other kernels (one commit group per tile).
     auto issue_tile = [&](int tile_index, unsigned seq) {
       const int stage = seq % D8_STAGES;
-      load_kv_tile<D8_BN, D8_NT>(p, sk + (size_t)stage * D8_BN * PITCH, sv + (size_t)stage * D8_BN * PITCH,
-                                 row_src[stage], begin + tile_index * D8_BN, kv_lo, end, b, m);
-    };
-#else
-    // Thread i < D8_BN brings row i of a tile: both of its rows with one bulk copy each.
-    auto issue_tile = [&](int tile_index, unsigned seq) {
-      if (threadIdx.x >= D8_BN) return;
-      const int stage = seq % D8_STAGES;
-      const int j = begin + tile_index * D8_BN + threadIdx.x;
-      bf16* krow = sk + ((size_t)stage * D8_BN + threadIdx.x) * PITCH;
-      bf16* vrow = sv + ((size_t)stage * D8_BN + threadIdx.x) * PITCH;
-      long long src = -1;
-      if (j >= kv_lo && j < end) {
-        const int page_index = j / p.page_size;
-        const long long page = p.block_table[(size_t)b * p.max_pages + page_index];
-        if (page < 0 || page >= p.num_pages)
-          atomicOr(p.err, SB_ERR_BAD_PAGE);
-        else
-          src = (long long)(((size_t)page * 2 * p.num_kv_heads + m) * head_stride +
-                            (size_t)(j - page_index * p.page_size) * DH);
-      }
-      if (src >= 0) {
-        mbar_arrive_expect_tx(&full[stage], 2 * ROW_BYTES);
-        bulk_copy_row(krow, p.cache + src, ROW_BYTES, &full[stage]);
-        bulk_copy_row(vrow, p.cache + src + v_offset, ROW_BYTES, &full[stage]);
+      const int j0 = begin + tile_index * D8_BN;
+      if (USE_TMA) {
+        // One thread: a box per page piece and 64-column slab, for keys and for values.  Boxes of
+        // pages the request does not hold, or wholly outside [kv_lo, end), are not fetched; the
+        // consumers zero what they must not read.
+        if (threadIdx.x != 0) return;
+        int boxes = 0;
+        for (int r = 0; r < D8_BN; r += box_rows) {
+          const int j = j0 + r;
+          if (j >= end || j + box_rows <= kv_lo) continue;
+          const long long page = p.block_table[(size_t)b * p.max_pages + j / p.page_size];
+          if (page >= 0 && page < p.num_pages) ++boxes;
+        }
+        mbar_arrive_expect_tx(&full[stage], boxes * 2 * SLABS * box_rows * 128);
+        for (int r = 0; r < D8_BN; r += box_rows) {
+          const int j = j0 + r;
+          if (j >= end || j + box_rows <= kv_lo) continue;
+          const long long page = p.block_table[(size_t)b * p.max_pages + j / p.page_size];
+          if (page < 0 || page >= p.num_pages) {
+            atomicOr(p.err, SB_ERR_BAD_PAGE);
+            continue;
+          }
+          const long long krow = ((page * 2) * p.num_kv_heads + m) * p.page_size + (j & (p.page_size - 1));
+          const long long vrow = krow + (long long)p.num_kv_heads * p.page_size;
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_box(sk + (size_t)stage * TILE_ELEMS + sl * SLAB_ELEMS + r * 64, &tmap, sl * 64, (int)krow, &full[stage]);
+            tma_load_box(sv + (size_t)stage * TILE_ELEMS + sl * SLAB_ELEMS + r * 64, &tmap, sl * 64, (int)vrow, &full[stage]);
+          }
+        }
       } else {
-        // Not a key of this request: its value row must read as zeros (0 * garbage could be NaN);
-        // its key row is masked by position whatever it holds.
-        for (int c = 0; c < CPR; ++c) *reinterpret_cast<uint4*>(vrow + c * 8) = make_uint4(0, 0, 0, 0);
-        for (int c = 0; c < CPR; ++c) *reinterpret_cast<uint4*>(krow + c * 8) = make_uint4(0, 0, 0, 0);
-        mbar_arrive(&full[stage]);
+        load_kv_tile<D8_BN, D8_NT>(p, sk + (size_t)stage * TILE_ELEMS, sv + (size_t)stage * TILE_ELEMS, row_src[stage],
+                                   j0, kv_lo, end, b, m);
       }
     };
-#endif
 
-#if SB_D8_BULK
-    for (int st = 0; st < D8_STAGES - 1 && st < n_tiles; ++st) issue_tile(st, tile_seq + st);
-#else
     for (int st = 0; st < D8_STAGES - 1; ++st) {
       if (st < n_tiles) issue_tile(st, tile_seq + st);
-      cp_async_commit();
+      if (!USE_TMA) cp_async_commit();
     }
-#endif
 
     // Queries: the 8-column operand, in registers for the whole chunk.  Column g is query row g.
     uint32_t qf[DH / 16][2];
@@ -612,89 +624,101 @@ __global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p,
     for (int it = 0; it < n_tiles; ++it) {
       const unsigned seq = tile_seq + it;
       const int stage = seq % D8_STAGES;
-#if SB_D8_BULK
-      if (it + D8_STAGES - 1 < n_tiles) issue_tile(it + D8_STAGES - 1, seq + D8_STAGES - 1);
-      // A thread whose wait ran out skips the arithmetic; the block agrees on leaving at the barrier below.
-      const bool landed = mbar_wait_bounded(&full[stage], (seq / D8_STAGES) & 1);
-#else
-      cp_async_wait<D8_STAGES - 2>();
-      __syncthreads();  // tile `it` has landed for every thread; the stage of tile it - 1 is free
-      if (it + D8_STAGES - 1 < n_tiles) issue_tile(it + D8_STAGES - 1, seq + D8_STAGES - 1);
-      cp_async_commit();
-      const bool landed = true;
-#endif
+      bool landed = true;
+      if (USE_TMA) {
+        // The stage refilled here was read in the last iteration; the barrier at its end freed it.
+        if (it + D8_STAGES - 1 < n_tiles) issue_tile(it + D8_STAGES - 1, seq + D8_STAGES - 1);
+        // A thread whose wait ran out skips the arithmetic; the block agrees on leaving below.
+        landed = mbar_wait_bounded(&full[stage], (seq / D8_STAGES) & 1);
+      } else {
+        cp_async_wait<D8_STAGES - 2>();
+        __syncthreads();  // tile `it` has landed for every thread; the stage of tile it - 1 is free
+        if (it + D8_STAGES - 1 < n_tiles) issue_tile(it + D8_STAGES - 1, seq + D8_STAGES - 1);
+        cp_async_commit();
+      }
       if (landed) {
-      const bf16* kt = sk + ((size_t)stage * D8_BN + warp * 16) * PITCH;
-      const bf16* vt = sv + ((size_t)stage * D8_BN + warp * 16) * PITCH;
-      // scores^T for this warp's 16 keys; two accumulators so that the chain of mma's is half as long
-      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int ks = 0; ks < DH / 16; ks += 2) {
-        uint32_t a[4], a2[4];
-        ldmatrix_x4(a, kt + (lane & 15) * PITCH + ks * 16 + (lane >> 4) * 8);
-        mma16816(s0, a, qf[ks][0], qf[ks][1]);
-        if (ks + 1 < DH / 16) {
-          ldmatrix_x4(a2, kt + (lane & 15) * PITCH + (ks + 1) * 16 + (lane >> 4) * 8);
-          mma16816(s1, a2, qf[ks + 1][0], qf[ks + 1][1]);
+        const bf16* kt = sk + (size_t)stage * TILE_ELEMS;
+        const bf16* vt = sv + (size_t)stage * TILE_ELEMS;
+        const int key0 = warp * 16;  // this warp's keys of the tile
+        const int j_first = begin + it * D8_BN + key0;
+        if (USE_TMA && (j_first < kv_lo || j_first + 16 > end)) {
+          // Some of this warp's 16 keys are not the request's: their value rows must read as zeros
+          // (0 * garbage could be NaN).  Only this warp reads these rows.
+          for (int i = lane; i < 16 * (DH / 8); i += 32) {
+            const int r = i / (DH / 8), c = i - r * (DH / 8);
+            const int j = j_first + r;
+            if (j < kv_lo || j >= end)
+              *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<true>(vt, key0 + r, c * 8))) = make_uint4(0, 0, 0, 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          __syncwarp();
         }
-      }
-      // s[0]: (key g, row 2t)  s[1]: (key g, row 2t+1)  s[2]: (key g+8, row 2t)  s[3]: (key g+8, row 2t+1)
-      const int j_lo = begin + it * D8_BN + warp * 16 + g;
-      float sc[4];
+        // scores^T for this warp's 16 keys; two accumulators halve the chain of dependent mma's
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s0[e] + s1[e];
-        if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
-        const int j = j_lo + (e >> 1) * 8;
-        const int pos = (e & 1) ? pos1 : pos0;
-        const bool keep = j <= pos && (p.window <= 0 || pos - j < p.window);
-        sc[e] = keep ? v * LOG2E : -INFINITY;
-      }
-      float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+        for (int ks = 0; ks < DH / 16; ks += 2) {
+          uint32_t a[4], a2[4];
+          ldmatrix_x4(a, tile_at<USE_TMA>(kt, key0 + (lane & 15), ks * 16 + (lane >> 4) * 8));
+          mma16816(s0, a, qf[ks][0], qf[ks][1]);
+          if (ks + 1 < DH / 16) {
+            ldmatrix_x4(a2, tile_at<USE_TMA>(kt, key0 + (lane & 15), (ks + 1) * 16 + (lane >> 4) * 8));
+            mma16816(s1, a2, qf[ks + 1][0], qf[ks + 1][1]);
+          }
+        }
+        // s[0]: (key g, row 2t)  s[1]: (key g, row 2t+1)  s[2]: (key g+8, row 2t)  s[3]: (key g+8, row 2t+1)
+        float sc[4];
 #pragma unroll
-      for (int off = 4; off < 32; off <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-      }
-      const float new0 = fmaxf(m0, mx0), new1 = fmaxf(m1, mx1);
-      const float use0 = new0 == -INFINITY ? 0.f : new0, use1 = new1 == -INFINITY ? 0.f : new1;
-      const float alpha0 = fast_exp2(m0 - use0), alpha1 = fast_exp2(m1 - use1);
-      m0 = new0;
-      m1 = new1;
-      const float p0 = fast_exp2(sc[0] - use0), p1 = fast_exp2(sc[1] - use1);
-      const float p2 = fast_exp2(sc[2] - use0), p3 = fast_exp2(sc[3] - use1);
-      l0 = l0 * alpha0 + p0 + p2;  // this thread's keys only; the eight g-lanes are added at the end
-      l1 = l1 * alpha1 + p1 + p3;
-      if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+        for (int e = 0; e < 4; ++e) {
+          float v = s0[e] + s1[e];
+          if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
+          const int j = j_first + g + (e >> 1) * 8;
+          const int pos = (e & 1) ? pos1 : pos0;
+          const bool keep = j <= pos && (p.window <= 0 || pos - j < p.window);
+          sc[e] = keep ? v * LOG2E : -INFINITY;
+        }
+        float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float new0 = fmaxf(m0, mx0), new1 = fmaxf(m1, mx1);
+        const float use0 = new0 == -INFINITY ? 0.f : new0, use1 = new1 == -INFINITY ? 0.f : new1;
+        const float alpha0 = fast_exp2(m0 - use0), alpha1 = fast_exp2(m1 - use1);
+        m0 = new0;
+        m1 = new1;
+        const float p0 = fast_exp2(sc[0] - use0), p1 = fast_exp2(sc[1] - use1);
+        const float p2 = fast_exp2(sc[2] - use0), p3 = fast_exp2(sc[3] - use1);
+        l0 = l0 * alpha0 + p0 + p2;  // this thread's keys only; the eight g-lanes are added at the end
+        l1 = l1 * alpha1 + p1 + p3;
+        if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+#pragma unroll
+          for (int d = 0; d < DH / 16; ++d) {
+            o[d][0] *= alpha0;
+            o[d][1] *= alpha1;
+            o[d][2] *= alpha0;
+            o[d][3] *= alpha1;
+          }
+        }
+        // P^T as the 8-column operand: (keys 2t, 2t+1 | 2t+8, 2t+9 ; row g) from (key g | g+8 ; rows 2t, 2t+1).
+        const uint32_t b0 = movmatrix_trans(pack_bf16(p0, p1));
+        const uint32_t b1 = movmatrix_trans(pack_bf16(p2, p3));
 #pragma unroll
         for (int d = 0; d < DH / 16; ++d) {
-          o[d][0] *= alpha0;
-          o[d][1] *= alpha1;
-          o[d][2] *= alpha0;
-          o[d][3] *= alpha1;
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, tile_at<USE_TMA>(vt, key0 + ((lane >> 4) & 1) * 8 + (lane & 7), d * 16 + ((lane >> 3) & 1) * 8));
+          mma16816(o[d], a, b0, b1);
         }
       }
-      // P^T as the 8-column operand: (keys 2t, 2t+1 | 2t+8, 2t+9 ; row g) from (key g | g+8 ; rows 2t, 2t+1).
-      const uint32_t b0 = movmatrix_trans(pack_bf16(p0, p1));
-      const uint32_t b1 = movmatrix_trans(pack_bf16(p2, p3));
-#pragma unroll
-      for (int d = 0; d < DH / 16; ++d) {
-        uint32_t a[4];
-        ldmatrix_x4_trans(a, vt + (((lane >> 4) & 1) * 8 + (lane & 7)) * PITCH + d * 16 + ((lane >> 3) & 1) * 8);
-        mma16816(o[d], a, b0, b1);
+      if (USE_TMA) {
+        // Everyone is done with this stage before it is filled again; and did everyone get its tile?
+        if (!__syncthreads_and(landed ? 1 : 0)) {
+          ok = false;
+          break;
+        }
       }
-      }
-#if SB_D8_BULK
-      // Everyone is done with this stage before it is filled again; and did everyone get its tile?
-      if (!__syncthreads_and(landed ? 1 : 0)) {
-        ok = false;
-        break;
-      }
-#endif
     }
-#if !SB_D8_BULK
-    cp_async_wait<0>();
-#endif
+    if (!USE_TMA) cp_async_wait<0>();
     if (!ok) {
       atomicOr(p.err, SB_ERR_TIMEOUT);
       s_failed = 1;
@@ -702,8 +726,8 @@ __global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p,
     tile_seq += n_tiles;
     __syncthreads();
     if (s_failed) {
-      // Copies of this block may still be in flight: give them a bounded time to land, then leave.
-      for (int st = 0; st < D8_STAGES; ++st) mbar_wait_bounded(&full[st], 0);
+      // Copies of this block may still be in flight: give them a millisecond to land, then leave.
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
       break;
     }
 #pragma unroll
@@ -754,8 +778,8 @@ __global__ void __launch_bounds__(D8_NT) attn_decode8_kernel(const AttnParams p,
         p.part_ml[(pidx * p.rows_max + r) * 2 + 1] = den;
       }
     }
-    // The generic-proxy writes above must not be overtaken by the next item's bulk copies.
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    // The generic-proxy writes above must not be overtaken by the next item's asynchronous copies.
+    if (USE_TMA) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
 }
 
@@ -828,10 +852,26 @@ constexpr size_t DECODE_SMEM_MERGE =
     16 * PITCH * sizeof(bf16) + (size_t)(2 * DEC_WARPS * 16 + DEC_WARPS * 16 * DH) * sizeof(float);
 constexpr size_t DECODE_SMEM = DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE;
 constexpr size_t DECODE8_SMEM_KV = (size_t)(2 * D8_STAGES * D8_BN) * PITCH * sizeof(bf16);
+constexpr size_t DECODE8_SMEM_TMA_KV = (size_t)(2 * D8_STAGES * D8_BN) * DH * sizeof(bf16);
 constexpr size_t DECODE8_SMEM_MERGE = (size_t)(2 * D8_WARPS * 8 + D8_WARPS * 8 * DH) * sizeof(float);
 constexpr size_t DECODE8_SMEM = DECODE8_SMEM_KV > DECODE8_SMEM_MERGE ? DECODE8_SMEM_KV : DECODE8_SMEM_MERGE;
 
 }  // namespace
+
+// Opts the kernel in to `smem` bytes of dynamic shared memory and reports how many of its
+// blocks the device holds at once.
+template <typename Kernel>
+static int blocks_resident(Kernel kernel, int threads, size_t smem, int* out) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  int per_sm = 0, sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
+  if (e != cudaSuccess) return (int)e;
+  *out = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
+  return 0;
+}
 
 #define SB_CONCAT2(a, b) a##b
 #define SB_CONCAT(a, b) SB_CONCAT2(a, b)
@@ -872,8 +912,9 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
                                      int num_pages, float cap, int window, const int* items, int num_items,
                                      int chunk, float* part_o, float* part_ml, int* work_counter,
                                      int rows_max, const int* split_start, const int* split_count, int variant,
-                                     int* err, cudaStream_t stream) {
-  // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel); 16 forces the 16-row kernel.
+                                     const void* tensor_map, int* err, cudaStream_t stream) {
+  // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel, fed by TMA when a
+  // tensor map is given and the shapes allow); 1 forbids TMA; 16 forces the 16-row kernel.
   if (num_items == 0) return 0;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || rows_max > 16 || chunk % 64) return -8;
   AttnParams p{};
@@ -882,35 +923,36 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.chunk = chunk; p.part_o = part_o; p.part_ml = part_ml;
   p.rows_max = rows_max; p.err = err;
-  static int resident = 0;  // blocks of this kernel the device holds at once
-  if (resident == 0) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)DECODE_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    int per_sm = 0, sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, DEC_NT, DECODE_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    resident = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
-  }
-  static int resident8 = 0;
-  if (resident8 == 0) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)DECODE8_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    int per_sm = 0, sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode8_kernel, D8_NT, DECODE8_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    resident8 = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 1);
-  }
   const int total_work = num_items * num_kv_heads;
-  if (rows_max <= 8 && variant != 16) {
-    sb_launch(attn_decode8_kernel, total_work < resident8 ? total_work : resident8, D8_NT, DECODE8_SMEM, stream,
-        p, work_counter, total_work);
+  const bool power_of_two_pages = (page_size & (page_size - 1)) == 0;
+  if (rows_max <= 8 && variant != 16 && TMA_OK && tensor_map != nullptr && power_of_two_pages && variant != 1) {
+    static int resident_tma = 0;
+    constexpr size_t smem = (DECODE8_SMEM_TMA_KV > DECODE8_SMEM_MERGE ? DECODE8_SMEM_TMA_KV : DECODE8_SMEM_MERGE) + 1024;
+    if (resident_tma == 0) {
+      int rc = blocks_resident(attn_decode8_kernel<true>, D8_NT, smem, &resident_tma);
+      if (rc) return rc;
+    }
+    CUtensorMap map;
+    memcpy(&map, tensor_map, sizeof(map));
+    const int box_rows = page_size < D8_BN ? page_size : D8_BN;
+    sb_launch(attn_decode8_kernel<true>, total_work < resident_tma ? total_work : resident_tma, D8_NT, smem, stream,
+        p, work_counter, total_work, map, box_rows);
+  } else if (rows_max <= 8 && variant != 16) {
+    static int resident8 = 0;
+    if (resident8 == 0) {
+      int rc = blocks_resident(attn_decode8_kernel<false>, D8_NT, DECODE8_SMEM, &resident8);
+      if (rc) return rc;
+    }
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    sb_launch(attn_decode8_kernel<false>, total_work < resident8 ? total_work : resident8, D8_NT, DECODE8_SMEM, stream,
+        p, work_counter, total_work, map, 0);
   } else {
+    static int resident = 0;  // blocks of this kernel the device holds at once
+    if (resident == 0) {
+      int rc = blocks_resident(attn_decode_kernel, DEC_NT, DECODE_SMEM, &resident);
+      if (rc) return rc;
+    }
     sb_launch(attn_decode_kernel, total_work < resident ? total_work : resident, DEC_NT, DECODE_SMEM, stream,
         p, work_counter, total_work);
   }
@@ -919,5 +961,35 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
       part_o, part_ml, token_seq, cu_q, split_start, split_count, (bf16*)out, num_q_heads, num_kv_heads,
       rows_max, work_counter);
   SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Writes into `map_out` (128 bytes, host memory) the tensor map of one cache storage
+// [pages, 2, heads, page_size, DH] seen as a matrix of total_rows x DH, fetched in boxes of
+// box_rows x 64 elements with the 128-byte swizzle.  Returns 0, -11 when the head size does
+// not allow it (not a multiple of 64), or -12 when the driver refuses.
+extern "C" int SB_FN(sb_attn_tensor_map)(void* map_out, const void* cache, long long total_rows, int box_rows) {
+  if (!TMA_OK || box_rows <= 0 || box_rows > 256) return -11;
+  typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiled encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess || !fn)
+      return -12;
+    encode = (EncodeTiled)fn;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)DH, (cuuint64_t)total_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)DH * sizeof(bf16)};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  CUtensorMap map;
+  const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box,
+                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -12;
+  memcpy(map_out, &map, sizeof(map));
   return 0;
 }

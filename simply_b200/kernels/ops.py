@@ -79,6 +79,7 @@ class CudaOps:
     self._declare()
     self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
     self._attn_fns: dict[int, tuple] = {}
+    self._tensor_maps: dict[tuple, tuple] = {}
     # Work counter of the split-key attention kernel: zero between launches (its merge kernel resets it).
     self._attn_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
     # bfloat16 attention runs on tensor cores where the shape allows; False forces the general kernel.
@@ -87,7 +88,7 @@ class CudaOps:
     # decode_chunk > 0 fixes the chunk length instead (a multiple of 64).
     self.decode_target_items = 148 * 2
     self.decode_chunk = 0
-    # 0: the kernel is picked by the number of query rows; 16 forces the 16-row kernel (tests).
+    # 0: the kernel is picked by the number of query rows; 1 forbids TMA; 16 forces the 16-row kernel (tests).
     self.decode_variant = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -171,9 +172,12 @@ class CudaOps:
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
                          c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_int,
-                         c_void, c_void, c_int, c_void, c_void]
+                         c_void, c_void, c_int, c_void, c_void, c_void]
       decode.restype = c_int
-      fns = self._attn_fns[head_dim] = (prefill, decode)
+      make_map = getattr(lib, f"sb_attn_tensor_map_hd{head_dim}")
+      make_map.argtypes = [c_void, c_void, ctypes.c_longlong, c_int]
+      make_map.restype = c_int
+      fns = self._attn_fns[head_dim] = (prefill, decode, make_map)
     return fns
 
   def decode_chunk_for(self, batch: int, kv_len: int) -> int:
@@ -212,6 +216,22 @@ class CudaOps:
       count[i] = n
     start = (np.arange(b) * items_per_seq).astype(np.int32)
     return items.reshape(-1, 2), start, count
+
+  def _tensor_map(self, storage: torch.Tensor, head_dim: int, page_size: int):
+    """TMA descriptor of a cache storage (made once per storage), or None where TMA cannot be used."""
+    if head_dim % 64 or page_size & (page_size - 1):
+      return None
+    key = (storage.data_ptr(), head_dim, page_size)
+    buf = self._tensor_maps.get(key)
+    if buf is None:
+      make_map = self._attention_lib(head_dim)[2]
+      buf = ctypes.create_string_buffer(128 + 64)
+      aligned = (ctypes.addressof(buf) + 63) & ~63
+      tile_keys = 32 if head_dim > 128 else 64
+      rc = make_map(ctypes.c_void_p(aligned), _ptr(storage), storage.numel() // head_dim, min(page_size, tile_keys))
+      buf = (buf, aligned if rc == 0 else None)
+      self._tensor_maps[key] = buf
+    return ctypes.c_void_p(buf[1]) if buf[1] is not None else None
 
   def _attention_plan(self, ctx: Any, window: int | None, group: int) -> dict:
     """Work lists of the two tensor-core kernels for this step, per (window, group).
@@ -410,7 +430,7 @@ class CudaOps:
     out = self._new(t, num_heads * head_dim, dtype=q.dtype)
     group = num_heads // num_kv_heads
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
-      prefill, decode = self._attention_lib(head_dim)
+      prefill, decode, _ = self._attention_lib(head_dim)
       plan = self._attention_plan(ctx, window, group)
       common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
                 _ptr(ctx.q_start))
@@ -428,8 +448,8 @@ class CudaOps:
         rc = decode(*common, _ptr(ctx.token_seq), _ptr(out), t, *sizes, _ptr(plan["decode_items"]),
                     plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), _ptr(self._attn_counter),
                     plan["rows_max"],
-                    _ptr(plan["split_start"]), _ptr(plan["split_count"]), self.decode_variant, _ptr(self.err),
-                    self._stream())
+                    _ptr(plan["split_start"]), _ptr(plan["split_count"]), self.decode_variant,
+                    self._tensor_map(storage, head_dim, ctx.page_size), _ptr(self.err), self._stream())
         self.launches += 2
         if rc:
           raise KernelError(f"sb_attn_decode: {_STATUS.get(rc, rc)}")
