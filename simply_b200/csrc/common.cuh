@@ -122,19 +122,21 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 #include <stdlib.h>
 
-// SIMPLY_B200_PDL=0 in the environment launches every kernel the plain way.
-inline bool sb_pdl_enabled() {
-  static int enabled = -1;
-  if (enabled < 0) {
+// SIMPLY_B200_PDL in the environment: 0 launches every kernel the plain way, 1 lets every
+// kernel start early, 2 (the default) only those that have something to do before their
+// inputs are ready (the weight-streaming products).
+inline int sb_pdl_level() {
+  static int level = -1;
+  if (level < 0) {
     const char* e = getenv("SIMPLY_B200_PDL");
-    enabled = (e && e[0] == '0') ? 0 : 1;
+    level = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
   }
-  return enabled == 1;
+  return level;
 }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args... args) {
+inline cudaError_t sb_launch_level(int min_level, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -144,8 +146,23 @@ inline cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = sb_pdl_enabled() ? 1 : 0;
+  const int level = sb_pdl_level();
+  config.numAttrs = (level == 1 || (level == 2 && min_level == 2)) ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
+// A kernel that gains nothing from starting early.
+template <typename... KArgs, typename... Args>
+inline cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  return sb_launch_level(1, kernel, grid, block, smem, stream, args...);
+}
+
+// A kernel that fetches data no earlier kernel writes (weights) before it waits for its inputs.
+template <typename... KArgs, typename... Args>
+inline cudaError_t sb_launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t stream, Args... args) {
+  return sb_launch_level(2, kernel, grid, block, smem, stream, args...);
 }
 
 #define SB_LAUNCH_CHECK()                      \

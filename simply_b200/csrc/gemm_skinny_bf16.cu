@@ -170,13 +170,13 @@ static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, 
   const int n_out = epilogue == 2 ? N / 2 : N;
   const unsigned blocks = (unsigned)((n_out + 15) / 16);
   if (epilogue == 0)
-    sb_launch(skinny_gemm_kernel<MT, WARPS, 0>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+    sb_launch_early(skinny_gemm_kernel<MT, WARPS, 0>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
         act);
   else if (epilogue == 1)
-    sb_launch(skinny_gemm_kernel<MT, WARPS, 1>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+    sb_launch_early(skinny_gemm_kernel<MT, WARPS, 1>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
         act);
   else
-    sb_launch(skinny_gemm_kernel<MT, WARPS, 2>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+    sb_launch_early(skinny_gemm_kernel<MT, WARPS, 2>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
         act);
   SB_LAUNCH_CHECK();
   return 0;
