@@ -230,25 +230,29 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
 }
 
 // ---------------------------------------------------------------------------------------
-// Prefill: grid (items, kv heads), 128 threads.
+// Prefill: grid (items, kv heads); WARPS warps of 16 query rows each (4 or 8: tiles of 64 or
+// 128 query rows; the larger tile halves the key/value traffic per row and gives every
+// scheduler two warps to switch between).
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(const AttnParams p) {
+  constexpr int BM = WARPS * 16, THREADS = WARPS * 32;
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [64][PITCH]
-  bf16* sk = sq + 64 * PITCH;                    // [2][BN][PITCH]
+  bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [BM][PITCH]
+  bf16* sk = sq + BM * PITCH;                    // [2][BN][PITCH]
   bf16* sv = sk + 2 * BN * PITCH;                // [2][BN][PITCH]
   __shared__ long long row_src[2][BN];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int b = p.items[2 * blockIdx.x], i0 = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
   const int group = p.num_q_heads / p.num_kv_heads;
-  const int tokens_per_tile = 64 / group;
+  const int tokens_per_tile = BM / group;
   const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
   const int ntok = min(tokens_per_tile, q_len - i0);
   const int rows_valid = ntok * group;
 
-  for (int i = threadIdx.x; i < 64 * CPR; i += NT) {
+  for (int i = threadIdx.x; i < BM * CPR; i += THREADS) {
     const int row = i / CPR, c = i - row * CPR;
     const bool valid = row < rows_valid;
     const int tok = valid ? i0 + row / group : i0, h = m * group + (valid ? row % group : 0);
@@ -260,7 +264,7 @@ __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
   const int kv_hi = p1 + 1;
   const int tile0 = (lo / BN) * BN;
   const int n_tiles = (kv_hi - tile0 + BN - 1) / BN;
-  load_kv_tile<BN, NT>(p, sk, sv, row_src[0], tile0, kv_lo, kv_hi, b, m);
+  load_kv_tile<BN, THREADS>(p, sk, sv, row_src[0], tile0, kv_lo, kv_hi, b, m);
   cp_async_commit();
 
   const int ra = warp * 16 + g, rb = ra + 8;
@@ -274,7 +278,7 @@ __global__ void __launch_bounds__(NT) attn_prefill_kernel(const AttnParams p) {
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it & 1;
     if (it + 1 < n_tiles) {
-      load_kv_tile<BN, NT>(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, row_src[stage ^ 1],
+      load_kv_tile<BN, THREADS>(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, row_src[stage ^ 1],
                            tile0 + (it + 1) * BN, kv_lo, kv_hi, b, m);
       cp_async_commit();
       cp_async_wait<1>();
@@ -846,7 +850,7 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     op[d] = __float2bfloat16_rn(((s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d])) * inv);
 }
 
-constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BN) * PITCH * sizeof(bf16);
+constexpr size_t prefill_smem(int rows) { return (size_t)(rows + 4 * BN) * PITCH * sizeof(bf16); }
 constexpr size_t DECODE_SMEM_KV = (size_t)(16 + 2 * DEC_STAGES * DEC_BN) * PITCH * sizeof(bf16);
 constexpr size_t DECODE_SMEM_MERGE =
     16 * PITCH * sizeof(bf16) + (size_t)(2 * DEC_WARPS * 16 + DEC_WARPS * 16 * DH) * sizeof(float);
@@ -877,26 +881,41 @@ static int blocks_resident(Kernel kernel, int threads, size_t smem, int* out) {
 #define SB_CONCAT(a, b) SB_CONCAT2(a, b)
 #define SB_FN(name) SB_CONCAT(SB_CONCAT(name, _hd), SB_HEAD_DIM)
 
-// Ragged prefill attention.  items: [num_items, 2] (sequence, first token of a 64 / G token tile).
+// Ragged prefill attention.  items: [num_items, 2] (sequence, first token of a tile of
+// rows_per_tile / G tokens); rows_per_tile is 64 or 128.
 extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const int* block_table, int max_pages,
                                       const int* cu_q, const int* q_start, void* out, int num_q_heads,
                                       int num_kv_heads, int page_size, int num_pages, float cap, int window,
-                                      const int* items, int num_items, int* err, cudaStream_t stream) {
+                                      const int* items, int num_items, int rows_per_tile, int* err,
+                                      cudaStream_t stream) {
   if (num_items == 0) return 0;
-  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > 64) return -8;
+  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > rows_per_tile) return -8;
   AttnParams p{};
   p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.err = err;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)PREFILL_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
+  if (rows_per_tile == 128) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)prefill_smem(128));
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    sb_launch(attn_prefill_kernel<8>, dim3(num_items, num_kv_heads), 256, prefill_smem(128), stream, p);
+  } else if (rows_per_tile == 64) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)prefill_smem(64));
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    sb_launch(attn_prefill_kernel<4>, dim3(num_items, num_kv_heads), 128, prefill_smem(64), stream, p);
+  } else {
+    return -8;
   }
-  sb_launch(attn_prefill_kernel, dim3(num_items, num_kv_heads), NT, PREFILL_SMEM, stream, p);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -113,7 +113,7 @@ class DecodeRunner:
     plans = {}
     for (window, group), per_seq in items_per_seq.items():
       plans[(window, group)] = dict(
-          num_prefill=0, num_decode=batch * per_seq, chunk=chunk, rows_max=group,
+          num_prefill=0, num_decode=batch * per_seq, chunk=chunk, rows_max=group, rows_per_tile=64,
           prefill_items=None, decode_items=view(f"items{window}_{group}"),
           split_start=view(f"split_start{window}_{group}"), split_count=view(f"split_count{window}_{group}"))
     sampled = torch.zeros(batch, dtype=torch.int32, device=eng.device)

@@ -90,6 +90,8 @@ class CudaOps:
     self.decode_chunk = 0
     # 0: the kernel is picked by the number of query rows; 1 forbids TMA; 16 forces the 16-row kernel (tests).
     self.decode_variant = 0
+    # 0: prefill tiles of 128 query rows when a sequence fills them, else 64; 64 or 128 forces one.
+    self.prefill_rows = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
@@ -158,7 +160,7 @@ class CudaOps:
 
   def _uses_tensor_core_attention(self, head_dim: int, group: int) -> bool:
     return (self.dtype == torch.bfloat16 and self.tensor_core_attention and head_dim % 16 == 0
-            and head_dim <= 256 and group <= 64)
+            and head_dim <= 256 and group <= 64)  # a group must fit a 64-row tile
 
   def _attention_lib(self, head_dim: int):
     fns = self._attn_fns.get(head_dim)
@@ -167,7 +169,7 @@ class CudaOps:
       c_int, c_float, c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
       prefill = getattr(lib, f"sb_attn_prefill_hd{head_dim}")
       prefill.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
-                          c_float, c_int, c_void, c_int, c_void, c_void]
+                          c_float, c_int, c_void, c_int, c_int, c_void, c_void]
       prefill.restype = c_int
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
@@ -239,7 +241,7 @@ class CudaOps:
     Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
     split-key kernel: their keys are cut into chunks at multiples of `chunk` of the
     absolute position, one work item per chunk.  The others are cut into tiles of
-    64 // group tokens for the prefill kernel, heaviest tile first.
+    64 // group or 128 // group tokens for the prefill kernel, heaviest tile first.
     """
     key = ("attention_plan", window, group)
     plan = ctx.memo.get(key)
@@ -248,7 +250,9 @@ class CudaOps:
     cu_q, q_start = ctx.host["cu_q"], ctx.host["q_start"].astype(np.int64)
     q_len = np.diff(cu_q).astype(np.int64)
     small = q_len * group <= 16
-    tokens_per_tile = 64 // group
+    # Tiles of 128 query rows when a sequence fills them, else of 64.
+    rows_per_tile = self.prefill_rows or (128 if (q_len * group).max() >= 128 else 64)
+    tokens_per_tile = rows_per_tile // group
     num_seqs = len(q_len)
     pre = []
     for b in np.nonzero(~small)[0]:
@@ -279,7 +283,7 @@ class CudaOps:
     dev = torch.from_numpy(flat).to(self.device, non_blocking=True)
     n_pre, n_dec = prefill_items.size, decode_items.size
     plan = dict(
-        num_prefill=len(prefill_items), num_decode=len(decode_items), chunk=chunk,
+        num_prefill=len(prefill_items), num_decode=len(decode_items), chunk=chunk, rows_per_tile=rows_per_tile,
         rows_max=int((q_len[dec] * group).max()) if len(dec) else 0,
         prefill_items=dev[:n_pre], decode_items=dev[n_pre:n_pre + n_dec],
         split_start=dev[n_pre + n_dec:n_pre + n_dec + num_seqs], split_count=dev[n_pre + n_dec + num_seqs:])
@@ -437,7 +441,7 @@ class CudaOps:
       sizes = (num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window or 0))
       if plan["num_prefill"]:
         rc = prefill(*common, _ptr(out), *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
-                     _ptr(self.err), self._stream())
+                     plan["rows_per_tile"], _ptr(self.err), self._stream())
         self.launches += 1
         if rc:
           raise KernelError(f"sb_attn_prefill: {_STATUS.get(rc, rc)}")

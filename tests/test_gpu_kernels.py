@@ -286,11 +286,17 @@ def test_paged_attention_random(table, dtype, hq, hkv, dh, ps, window, cap):
   sc = make_scenario(SEQS, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=dtype,
                      device="cuda", ops=ops, seed=5)
   q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 1.5).to(dtype).cuda()
-  got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
-  ops.check_errors()
-  assert torch.isfinite(got).all(), "a page the request does not hold was read"
   want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)
-  close(got, want, dtype, 2.0)
+  for rows in ((0,) if dtype == torch.float32 else (0, 64, 128)):  # query rows per prefill tile
+    ops.prefill_rows = rows if rows >= hq // hkv else 0
+    sc.ctx.memo.clear()
+    try:
+      got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+    finally:
+      ops.prefill_rows = 0
+    ops.check_errors()
+    assert torch.isfinite(got).all(), "a page the request does not hold was read"
+    close(got, want, dtype, 2.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
