@@ -185,23 +185,32 @@ static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, 
 // Returns -9 when the shape is outside what the kernel takes (the caller then
 // uses the library product): M > 32, K not a multiple of 8, N odd for the gated epilogue.
 extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, int epilogue,
-                                   float cap, int act, cudaStream_t stream) {
+                                   float cap, int act, int warps_override, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M > 32 || K % 8 != 0 || K <= 0 || epilogue < 0 || epilogue > 2) return -9;
   if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 2)) return -9;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)w;
   const int n_out = epilogue == 2 ? N / 2 : N;
-  // Few blocks: more warps per block so that enough loads are in flight per SM.
-  const bool wide = (n_out + 15) / 16 < 4 * 148 && K >= 16 * 32 * 4;
+  // Warps per block (the split of K).  All blocks should be resident at once, so that the
+  // stream of weights never waits for a second wave: about 100 registers per thread let an SM
+  // hold 512 threads, i.e. 148 blocks of 16 warps, 296 of 8 or 592 of 4.  `warps_override`
+  // (4, 8 or 16) is for experiments.
+  const int blocks = (n_out + 15) / 16;
+  int warps = blocks <= 148 ? 16 : blocks <= 296 ? 8 : 4;
+  if (K < warps * 32 * 4) warps = K >= 8 * 32 * 4 ? 8 : 4;  // every warp should have a full batch of loads
+  if (warps_override == 4 || warps_override == 8 || warps_override == 16) warps = warps_override;
   if (M <= 8) {
-    return wide ? launch_skinny<1, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream)
-                : launch_skinny<1, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    if (warps == 16) return launch_skinny<1, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    if (warps == 8) return launch_skinny<1, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    return launch_skinny<1, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
   }
   if (M <= 16) {
-    return wide ? launch_skinny<2, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream)
-                : launch_skinny<2, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    if (warps == 16) return launch_skinny<2, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    if (warps == 8) return launch_skinny<2, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    return launch_skinny<2, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
   }
-  // (8 warps only: with 16 the partial sums of the gated epilogue outgrow static shared memory.)
+  // (8 warps at most: with 16 the partial sums of the gated epilogue outgrow static shared memory.)
+  if (warps == 4) return launch_skinny<4, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
   return launch_skinny<4, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
 }

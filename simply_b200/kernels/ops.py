@@ -92,6 +92,8 @@ class CudaOps:
     self.decode_variant = 0
     # 0: prefill tiles of 128 query rows when a sequence fills them, else 64; 64 or 128 forces one.
     self.prefill_rows = 0
+    # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
+    self.skinny_warps = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
@@ -113,7 +115,7 @@ class CudaOps:
         "sb_gated_activation": [c_void, c_int, c_void, c_int, c_int, c_int, c_void],
         "sb_soft_cap": [c_void, c_float, c_ll, c_void],
         "sb_gemm_f32_nt": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_void],
-        "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void],
+        "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
@@ -320,7 +322,7 @@ class CudaOps:
     x = self.cast(x, torch.bfloat16)
     if m <= self.skinny_max_rows:
       out = self._new(m, n, dtype=torch.bfloat16)
-      if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w), _ptr(out), m, n, k, 0, 0.0, 0) == 0:
+      if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w), _ptr(out), m, n, k, 0, 0.0, 0, self.skinny_warps) == 0:
         return out
     return torch.mm(x, w.t())
 
@@ -331,7 +333,7 @@ class CudaOps:
     if w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m <= self.skinny_max_rows:
       out = self._new(m, n // 2, dtype=torch.bfloat16)
       if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n, k, 2, 0.0,
-                    activation) == 0:
+                    activation, self.skinny_warps) == 0:
         return out
     return self.gated_activation(self.linear(x, w_gate_up), activation)
 
@@ -358,7 +360,7 @@ class CudaOps:
     for r0 in range(0, r, chunk):
       rows = min(chunk, r - r0)
       self._call("sb_gemm_skinny_bf16", _ptr(x[r0:]), _ptr(table), _ptr(out[r0:]), rows, v, k, 1,
-                 float(cap), 0)
+                 float(cap), 0, self.skinny_warps)
     return out
 
   def gated_activation(self, gate_up: torch.Tensor, activation: int) -> torch.Tensor:
