@@ -502,7 +502,7 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 constexpr int D8_BN = DH > 128 ? 32 : 64;  // keys per tile
 constexpr int D8_WARPS = D8_BN / 16;
 constexpr int D8_NT = D8_WARPS * 32;
-constexpr int D8_STAGES = 3;
+constexpr int D8_STAGES = 2;
 constexpr bool TMA_OK = DH % 64 == 0;        // 128-byte swizzled boxes of 64 columns
 constexpr int SLABS = TMA_OK ? DH / 64 : 1;  // 64-column slabs of a tile in the swizzled layout
 constexpr int SLAB_ELEMS = D8_BN * 64;       // elements of one slab of one tile
