@@ -787,6 +787,305 @@ attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work, const
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same kernel with a producer warp.  One extra warp does nothing but draw work items and
+// issue their TMA copies, running ahead of the consumer warps across item boundaries, so
+// the stream of tiles does not stop while the consumers merge one item and start the next.
+//   work ring : the producer publishes item numbers (work_full / work_empty, 2 slots)
+//   tiles     : full[stage] (tile landed, TMA) / empty[stage] (every consumer warp has left it)
+// The consumers merge their partial results in the stage of the item's last tile and release
+// that stage only afterwards, so no extra shared memory is needed.
+// All waits are bounded; a wait that runs out sets SB_ERR_TIMEOUT and makes the warp leave.
+// ---------------------------------------------------------------------------------------
+constexpr int WS_STAGES = 2;
+constexpr int WS_RING = 2;
+constexpr int WS_NT = (D8_WARPS + 1) * 32;
+
+struct WsItem {
+  int b, m, begin, end, kv_lo, n_tiles, qs, q_len, row0;
+};
+
+__device__ __forceinline__ bool ws_item(const AttnParams& p, int work, WsItem& w) {
+  const int item = work / p.num_kv_heads;
+  w.m = work - item * p.num_kv_heads;
+  w.b = p.items[2 * item];
+  if (w.b < 0) return false;  // filler item of a fixed-size work list
+  const int chunk_index = p.items[2 * item + 1];
+  w.row0 = p.cu_q[w.b];
+  w.q_len = p.cu_q[w.b + 1] - w.row0;
+  w.qs = p.q_start[w.b];
+  w.kv_lo = p.window > 0 ? max(w.qs - p.window + 1, 0) : 0;
+  const int kv_hi = w.qs + w.q_len;
+  w.begin = max(chunk_index * p.chunk, (w.kv_lo / 64) * 64);
+  w.end = min((chunk_index + 1) * p.chunk, kv_hi);
+  w.n_tiles = w.end > w.begin ? (w.end - w.begin + D8_BN - 1) / D8_BN : 0;
+  return true;
+}
+
+__device__ __forceinline__ void mbar_arrive_one(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(WS_NT)
+attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, const __grid_constant__ CUtensorMap tmap,
+                      int box_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int TILE_ELEMS = D8_BN * DH;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* aligned = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  bf16* sk = reinterpret_cast<bf16*>(aligned);  // [STAGES] key tiles
+  bf16* sv = sk + WS_STAGES * TILE_ELEMS;       // [STAGES] value tiles
+  __shared__ __align__(8) uint64_t full[WS_STAGES], empty[WS_STAGES], work_full[WS_RING], work_empty[WS_RING];
+  __shared__ int work_ring[WS_RING];
+  __shared__ float wm[D8_WARPS * 8], wl[D8_WARPS * 8];  // per warp and query row: running max, sum
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int group = p.num_q_heads / p.num_kv_heads;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < WS_STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], D8_WARPS);
+    }
+    for (int i = 0; i < WS_RING; ++i) {
+      mbar_init(&work_full[i], 1);
+      mbar_init(&work_empty[i], D8_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == D8_WARPS) {
+    // ---- producer: one thread ------------------------------------------------------------
+    if (lane != 0) return;
+    unsigned seq = 0;  // tiles issued so far
+    for (unsigned wi = 0;; ++wi) {
+      const int work = atomicAdd(work_counter, 1);
+      const int slot = wi % WS_RING;
+      if (wi >= WS_RING && !mbar_wait_bounded(&work_empty[slot], (wi / WS_RING - 1) & 1)) {
+        atomicOr(p.err, SB_ERR_TIMEOUT);
+        return;
+      }
+      work_ring[slot] = work;
+      mbar_arrive_one(&work_full[slot]);  // release: the consumers see the slot's content
+      if (work >= total_work) return;
+      WsItem w;
+      if (!ws_item(p, work, w)) continue;
+      for (int ti = 0; ti < w.n_tiles; ++ti, ++seq) {
+        const int stage = seq % WS_STAGES;
+        if (seq >= WS_STAGES && !mbar_wait_bounded(&empty[stage], (seq / WS_STAGES - 1) & 1)) {
+          atomicOr(p.err, SB_ERR_TIMEOUT);
+          return;
+        }
+        const int j0 = w.begin + ti * D8_BN;
+        int boxes = 0;
+        for (int r = 0; r < D8_BN; r += box_rows) {
+          const int j = j0 + r;
+          if (j >= w.end || j + box_rows <= w.kv_lo) continue;
+          const long long page = p.block_table[(size_t)w.b * p.max_pages + j / p.page_size];
+          if (page >= 0 && page < p.num_pages) ++boxes;
+        }
+        mbar_arrive_expect_tx(&full[stage], boxes * 2 * SLABS * box_rows * 128);
+        for (int r = 0; r < D8_BN; r += box_rows) {
+          const int j = j0 + r;
+          if (j >= w.end || j + box_rows <= w.kv_lo) continue;
+          const long long page = p.block_table[(size_t)w.b * p.max_pages + j / p.page_size];
+          if (page < 0 || page >= p.num_pages) {
+            atomicOr(p.err, SB_ERR_BAD_PAGE);
+            continue;
+          }
+          const long long krow = ((page * 2) * p.num_kv_heads + w.m) * p.page_size + (j & (p.page_size - 1));
+          const long long vrow = krow + (long long)p.num_kv_heads * p.page_size;
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_box(sk + (size_t)stage * TILE_ELEMS + sl * SLAB_ELEMS + r * 64, &tmap, sl * 64, (int)krow, &full[stage]);
+            tma_load_box(sv + (size_t)stage * TILE_ELEMS + sl * SLAB_ELEMS + r * 64, &tmap, sl * 64, (int)vrow, &full[stage]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- consumers: D8_WARPS warps, 16 keys of every tile each ---------------------------------
+  unsigned seq = 0;  // tiles consumed so far
+  for (unsigned wi = 0;; ++wi) {
+    const int slot = wi % WS_RING;
+    if (!mbar_wait_bounded(&work_full[slot], (wi / WS_RING) & 1)) {
+      if (lane == 0) atomicOr(p.err, SB_ERR_TIMEOUT);
+      return;
+    }
+    const int work = work_ring[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive_one(&work_empty[slot]);
+    if (work >= total_work) return;
+    WsItem w;
+    if (!ws_item(p, work, w)) continue;
+    const int rows_valid = w.q_len * group;  // <= 8 by the host's routing
+    const size_t pidx = (size_t)(work / p.num_kv_heads) * p.num_kv_heads + w.m;
+    if (w.n_tiles == 0) {
+      // Nothing of this chunk is visible: an empty partial result.
+      if (warp == 0) {
+        for (int i = lane; i < rows_valid * DH; i += 32) p.part_o[pidx * p.rows_max * DH + i] = 0.f;
+        if (lane < rows_valid) {
+          p.part_ml[(pidx * p.rows_max + lane) * 2] = -INFINITY;
+          p.part_ml[(pidx * p.rows_max + lane) * 2 + 1] = 0.f;
+        }
+      }
+      continue;
+    }
+    uint32_t qf[DH / 16][2];
+    {
+      const bool valid = g < rows_valid;
+      const bf16* qrow = p.q + ((size_t)(w.row0 + (valid ? g / group : 0)) * p.num_q_heads + w.m * group +
+                                (valid ? g % group : 0)) * DH;
+#pragma unroll
+      for (int ks = 0; ks < DH / 16; ++ks) {
+        qf[ks][0] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+        qf[ks][1] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+      }
+    }
+    const int pos0 = 2 * t < rows_valid ? w.qs + (2 * t) / group : -1;
+    const int pos1 = 2 * t + 1 < rows_valid ? w.qs + (2 * t + 1) / group : -1;
+    const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[DH / 16][4];
+#pragma unroll
+    for (int d = 0; d < DH / 16; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    int last_stage = 0;
+    for (int it = 0; it < w.n_tiles; ++it, ++seq) {
+      const int stage = seq % WS_STAGES;
+      last_stage = stage;
+      if (!mbar_wait_bounded(&full[stage], (seq / WS_STAGES) & 1)) {
+        if (lane == 0) atomicOr(p.err, SB_ERR_TIMEOUT);
+        return;
+      }
+      const bf16* kt = sk + (size_t)stage * TILE_ELEMS;
+      const bf16* vt = sv + (size_t)stage * TILE_ELEMS;
+      const int key0 = warp * 16;
+      const int j_first = w.begin + it * D8_BN + key0;
+      if (j_first < w.kv_lo || j_first + 16 > w.end) {
+        // Value rows of keys that are not the request's must read as zeros (only this warp reads them).
+        for (int i = lane; i < 16 * (DH / 8); i += 32) {
+          const int r = i / (DH / 8), c = i - r * (DH / 8);
+          const int j = j_first + r;
+          if (j < w.kv_lo || j >= w.end)
+            *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<true>(vt, key0 + r, c * 8))) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < DH / 16; ks += 2) {
+        uint32_t a[4], a2[4];
+        ldmatrix_x4(a, tile_at<true>(kt, key0 + (lane & 15), ks * 16 + (lane >> 4) * 8));
+        mma16816(s0, a, qf[ks][0], qf[ks][1]);
+        if (ks + 1 < DH / 16) {
+          ldmatrix_x4(a2, tile_at<true>(kt, key0 + (lane & 15), (ks + 1) * 16 + (lane >> 4) * 8));
+          mma16816(s1, a2, qf[ks + 1][0], qf[ks + 1][1]);
+        }
+      }
+      float sc[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s0[e] + s1[e];
+        if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
+        const int j = j_first + g + (e >> 1) * 8;
+        const int pos = (e & 1) ? pos1 : pos0;
+        const bool keep = j <= pos && (p.window <= 0 || pos - j < p.window);
+        sc[e] = keep ? v * LOG2E : -INFINITY;
+      }
+      float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float new0 = fmaxf(m0, mx0), new1 = fmaxf(m1, mx1);
+      const float use0 = new0 == -INFINITY ? 0.f : new0, use1 = new1 == -INFINITY ? 0.f : new1;
+      const float alpha0 = fast_exp2(m0 - use0), alpha1 = fast_exp2(m1 - use1);
+      m0 = new0;
+      m1 = new1;
+      const float p0 = fast_exp2(sc[0] - use0), p1 = fast_exp2(sc[1] - use1);
+      const float p2 = fast_exp2(sc[2] - use0), p3 = fast_exp2(sc[3] - use1);
+      l0 = l0 * alpha0 + p0 + p2;
+      l1 = l1 * alpha1 + p1 + p3;
+      if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+#pragma unroll
+        for (int d = 0; d < DH / 16; ++d) {
+          o[d][0] *= alpha0;
+          o[d][1] *= alpha1;
+          o[d][2] *= alpha0;
+          o[d][3] *= alpha1;
+        }
+      }
+      const uint32_t b0 = movmatrix_trans(pack_bf16(p0, p1));
+      const uint32_t b1 = movmatrix_trans(pack_bf16(p2, p3));
+#pragma unroll
+      for (int d = 0; d < DH / 16; ++d) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, tile_at<true>(vt, key0 + ((lane >> 4) & 1) * 8 + (lane & 7), d * 16 + ((lane >> 3) & 1) * 8));
+        mma16816(o[d], a, b0, b1);
+      }
+      if (it + 1 < w.n_tiles) {  // the last tile's stage is kept for the merge
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // (after the zeroing above, if any)
+        __syncwarp();
+        if (lane == 0) mbar_arrive_one(&empty[stage]);
+      }
+    }
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    // Merge the consumer warps in the last tile's stage: all have left it when the first
+    // consumer barrier is passed (the producer cannot refill it before `empty` is signalled).
+    asm volatile("bar.sync 1, %0;\n" ::"n"(D8_WARPS * 32) : "memory");
+    float* wo = reinterpret_cast<float*>(sk + (size_t)last_stage * TILE_ELEMS);  // [W][rows_valid][DH]
+    if (g == 0) {
+      wm[warp * 8 + 2 * t] = m0;
+      wm[warp * 8 + 2 * t + 1] = m1;
+      wl[warp * 8 + 2 * t] = l0;
+      wl[warp * 8 + 2 * t + 1] = l1;
+    }
+#pragma unroll
+    for (int d = 0; d < DH / 16; ++d) {
+      if (2 * t < rows_valid) {
+        wo[((size_t)warp * rows_valid + 2 * t) * DH + d * 16 + g] = o[d][0];
+        wo[((size_t)warp * rows_valid + 2 * t) * DH + d * 16 + g + 8] = o[d][2];
+      }
+      if (2 * t + 1 < rows_valid) {
+        wo[((size_t)warp * rows_valid + 2 * t + 1) * DH + d * 16 + g] = o[d][1];
+        wo[((size_t)warp * rows_valid + 2 * t + 1) * DH + d * 16 + g + 8] = o[d][3];
+      }
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(D8_WARPS * 32) : "memory");
+    for (int i = threadIdx.x; i < rows_valid * DH; i += D8_WARPS * 32) {
+      const int r = i / DH, d = i - r * DH;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int x = 0; x < D8_WARPS; ++x) mx = fmaxf(mx, wm[x * 8 + r]);
+      float num = 0.f, den = 0.f;
+      if (mx != -INFINITY) {
+#pragma unroll
+        for (int x = 0; x < D8_WARPS; ++x) {
+          const float scale = fast_exp2(wm[x * 8 + r] - mx);
+          num += scale * wo[((size_t)x * rows_valid + r) * DH + d];
+          den += scale * wl[x * 8 + r];
+        }
+      }
+      p.part_o[(pidx * p.rows_max + r) * DH + d] = den > 0.f ? num / den : 0.f;
+      if (d == 0) {
+        p.part_ml[(pidx * p.rows_max + r) * 2] = mx;
+        p.part_ml[(pidx * p.rows_max + r) * 2 + 1] = den;
+      }
+    }
+    // Hand the stage back: the reads above are done, and the TMA must not overtake the writes.
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive_one(&empty[last_stage]);
+  }
+}
+
 // Merges the chunks of every (token, query head): one block each.  Its warps take the
 // chunks in turn (warp w: chunks w, w + 4, ...), then add up in a fixed order.
 constexpr int COMBINE_WARPS = 4;
@@ -932,8 +1231,9 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
                                      int chunk, float* part_o, float* part_ml, int* work_counter,
                                      int rows_max, const int* split_start, const int* split_count, int variant,
                                      const void* tensor_map, int* err, cudaStream_t stream) {
-  // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel, fed by TMA when a
-  // tensor map is given and the shapes allow); 1 forbids TMA; 16 forces the 16-row kernel.
+  // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel, fed by TMA through a
+  // producer warp when a tensor map is given and the shapes allow); 1 forbids TMA; 2 uses TMA
+  // without the producer warp; 16 forces the 16-row kernel.
   if (num_items == 0) return 0;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || rows_max > 16 || chunk % 64) return -8;
   AttnParams p{};
@@ -944,7 +1244,21 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
   p.rows_max = rows_max; p.err = err;
   const int total_work = num_items * num_kv_heads;
   const bool power_of_two_pages = (page_size & (page_size - 1)) == 0;
-  if (rows_max <= 8 && variant != 16 && TMA_OK && tensor_map != nullptr && power_of_two_pages && variant != 1) {
+  constexpr size_t ws_merge = (size_t)(D8_WARPS * 8 * DH) * sizeof(float);
+  constexpr bool ws_fits = ws_merge <= (size_t)D8_BN * DH * sizeof(bf16);  // the merge borrows one key tile
+  if (rows_max <= 8 && (variant == 0 || variant == 3) && TMA_OK && ws_fits && tensor_map != nullptr && power_of_two_pages) {
+    static int resident_ws = 0;
+    constexpr size_t smem = (size_t)(2 * WS_STAGES * D8_BN) * DH * sizeof(bf16) + 1024;
+    if (resident_ws == 0) {
+      int rc = blocks_resident(attn_decode8ws_kernel, WS_NT, smem, &resident_ws);
+      if (rc) return rc;
+    }
+    CUtensorMap map;
+    memcpy(&map, tensor_map, sizeof(map));
+    const int box_rows = page_size < D8_BN ? page_size : D8_BN;
+    sb_launch(attn_decode8ws_kernel, total_work < resident_ws ? total_work : resident_ws, WS_NT, smem, stream,
+        p, work_counter, total_work, map, box_rows);
+  } else if (rows_max <= 8 && variant != 16 && TMA_OK && tensor_map != nullptr && power_of_two_pages && variant != 1) {
     static int resident_tma = 0;
     constexpr size_t smem = (DECODE8_SMEM_TMA_KV > DECODE8_SMEM_MERGE ? DECODE8_SMEM_TMA_KV : DECODE8_SMEM_MERGE) + 1024;
     if (resident_tma == 0) {

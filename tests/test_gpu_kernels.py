@@ -268,7 +268,8 @@ def test_split_key_attention_chunks(table, chunk, rows, hq, hkv, dh, ps, window,
   ops.decode_chunk = chunk
   want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)
   try:
-    for variant in (0, 1, 16):  # by row count (TMA where it can), without TMA, the 16-row kernel
+    # by row count (TMA with a producer warp where it can), without TMA, TMA without the producer warp, the 16-row kernel
+    for variant in (0, 1, 2, 16):
       ops.decode_variant = variant
       got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
       ops.check_errors()
