@@ -58,9 +58,9 @@ def test_embed(table, dtype):
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("width", [72, 2304, 3000])
 @pytest.mark.parametrize("variant", ["pre_only", "post_pre", "add_only", "post_only", "rows"])
-def test_residual_norm(table, dtype, width, variant):
+@pytest.mark.parametrize("rows_total", [19, 150])  # a block per row; a warp per row
+def test_residual_norm(table, dtype, width, variant, rows_total):
   ops, ref = table[dtype], ReferenceOps(dtype)
-  rows_total = 19
   h = torch.randn(rows_total, width) * 3
   branch = (torch.randn(rows_total, width) * 2).to(dtype)
   post = norm_part(width, dtype, True, 1e-6, 1)
@@ -76,7 +76,7 @@ def test_residual_norm(table, dtype, width, variant):
     args = (branch, post, None)
   else:
     args = (branch, post, pre)
-    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32)
+    rows = torch.tensor([18, 0, 7, 7] if rows_total < 64 else [149, 0, 7, 7] + list(range(20, 100)), dtype=torch.int32)
 
   def cpu(p):
     return None if p is None else types.SimpleNamespace(weight=p.weight.cpu(), eps=p.eps, plus_one=p.plus_one)
