@@ -167,7 +167,7 @@ __device__ __forceinline__ void scores(float (&s)[NKT][4], const bf16* sq_rows, 
 template <int NKT>
 __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8][4], float& m_a, float& m_b,
                                            float& l_a, float& l_b, int pos_a, int pos_b, int j0, float cap,
-                                           int window, const bf16* sv, int key0) {
+                                           int window, const bf16* sv, int key0, bool need_mask = true) {
   const int lane = threadIdx.x & 31, t = lane & 3;
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
   float mx_a = -INFINITY, mx_b = -INFINITY;
@@ -179,7 +179,8 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
       const int pos = e < 2 ? pos_a : pos_b;
       float v = s[i][e];
       if (cap > 0.f) v = cap * fast_tanh(v * inv_cap);
-      const bool keep = j <= pos && (window <= 0 || pos - j < window);
+      // need_mask is false (for the whole warp) when every key of the tile is visible to every row.
+      const bool keep = !need_mask || (j <= pos && (window <= 0 || pos - j < window));
       v = keep ? v * LOG2E : -INFINITY;
       s[i][e] = v;
       if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
@@ -205,12 +206,14 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
   }
   l_a = l_a * alpha_a + sum_a;  // per-thread share of the row sum; the quad is added up at the end
   l_b = l_b * alpha_b + sum_b;
+  if (__any_sync(0xffffffffu, alpha_a != 1.f || alpha_b != 1.f)) {  // the running maxima rarely move
 #pragma unroll
-  for (int d = 0; d < DH / 8; ++d) {
-    o[d][0] *= alpha_a;
-    o[d][1] *= alpha_a;
-    o[d][2] *= alpha_b;
-    o[d][3] *= alpha_b;
+    for (int d = 0; d < DH / 8; ++d) {
+      o[d][0] *= alpha_a;
+      o[d][1] *= alpha_a;
+      o[d][2] *= alpha_b;
+      o[d][3] *= alpha_b;
+    }
   }
 #pragma unroll
   for (int kk = 0; kk < NKT / 2; ++kk) {
@@ -230,21 +233,23 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
 }
 
 // ---------------------------------------------------------------------------------------
-// Prefill: grid (items, kv heads); WARPS warps of 16 query rows each (4 or 8: tiles of 64 or
-// 128 query rows; the larger tile halves the key/value traffic per row and gives every
-// scheduler two warps to switch between).
+// Prefill: grid (items, kv heads).  A block owns WM * 16 query rows; its WM * WN warps are
+// laid out as WM row groups of 16 rows times WN key groups that split every 64-key tile
+// between them (WN = 2: two warps per scheduler to switch between; their partial results
+// are merged through shared memory at the end).
 // ---------------------------------------------------------------------------------------
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(const AttnParams p) {
-  constexpr int BM = WARPS * 16, THREADS = WARPS * 32;
+template <int WM, int WN>
+__global__ void __launch_bounds__(WM * WN * 32) attn_prefill_kernel(const AttnParams p) {
   pdl_launch_dependents();
   pdl_wait();
+  constexpr int BM = WM * 16, THREADS = WM * WN * 32, KEYS = BN / WN;  // keys of a tile per warp
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [BM][PITCH]
   bf16* sk = sq + BM * PITCH;                    // [2][BN][PITCH]
   bf16* sv = sk + 2 * BN * PITCH;                // [2][BN][PITCH]
   __shared__ long long row_src[2][BN];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int wm = warp % WM, wn = warp / WM;
   const int b = p.items[2 * blockIdx.x], i0 = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
   const int group = p.num_q_heads / p.num_kv_heads;
   const int tokens_per_tile = BM / group;
@@ -267,9 +272,12 @@ __global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(const AttnPara
   load_kv_tile<BN, THREADS>(p, sk, sv, row_src[0], tile0, kv_lo, kv_hi, b, m);
   cp_async_commit();
 
-  const int ra = warp * 16 + g, rb = ra + 8;
+  const int ra = wm * 16 + g, rb = ra + 8;
   const int pos_a = ra < rows_valid ? p0 + ra / group : -1;
   const int pos_b = rb < rows_valid ? p0 + rb / group : -1;
+  // Positions of this warp's first and last row, for deciding whether a tile needs masking.
+  const bool rows_full = wm * 16 + 15 < rows_valid;
+  const int warp_pos_lo = p0 + (wm * 16) / group, warp_pos_hi = p0 + (wm * 16 + 15) / group;
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
   float o[DH / 8][4];
 #pragma unroll
@@ -279,23 +287,62 @@ __global__ void __launch_bounds__(WARPS * 32) attn_prefill_kernel(const AttnPara
     const int stage = it & 1;
     if (it + 1 < n_tiles) {
       load_kv_tile<BN, THREADS>(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, row_src[stage ^ 1],
-                           tile0 + (it + 1) * BN, kv_lo, kv_hi, b, m);
+                                tile0 + (it + 1) * BN, kv_lo, kv_hi, b, m);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    float s[BN / 8][4];
-    scores<BN / 8>(s, sq + warp * 16 * PITCH, sk + stage * BN * PITCH, 0);
-    softmax_pv<BN / 8>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, tile0 + it * BN, p.cap, p.window,
-                       sv + stage * BN * PITCH, 0);
+    const int j0 = tile0 + it * BN + wn * KEYS;  // this warp's first key of the tile
+    // Every key visible to every row of the warp: below the lowest row's position, inside the
+    // highest row's window.
+    const bool need_mask = !rows_full || j0 + KEYS - 1 > warp_pos_lo || (p.window > 0 && warp_pos_hi - j0 >= p.window);
+    float s[KEYS / 8][4];
+    scores<KEYS / 8>(s, sq + wm * 16 * PITCH, sk + stage * BN * PITCH, wn * KEYS);
+    softmax_pv<KEYS / 8>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, j0, p.cap, p.window, sv + stage * BN * PITCH,
+                         wn * KEYS, need_mask);
     __syncthreads();
   }
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  if (WN > 1) {
+    // The key groups of a row group merge: warps of group 1 hand (max, sum, output) to group 0.
+    float* xm = reinterpret_cast<float*>(sk);  // [BM] max, [BM] sum, then [BM][DH] (the tiles are no longer needed)
+    float* xl = xm + BM;
+    float* xo = xl + BM;
+    if (wn == 1) {
+      if (t == 0) {
+        xm[ra] = m_a; xm[rb] = m_b;
+        xl[ra] = l_a; xl[rb] = l_b;
+      }
+#pragma unroll
+      for (int d = 0; d < DH / 8; ++d) {
+        *reinterpret_cast<float2*>(xo + (size_t)ra * DH + d * 8 + 2 * t) = make_float2(o[d][0], o[d][1]);
+        *reinterpret_cast<float2*>(xo + (size_t)rb * DH + d * 8 + 2 * t) = make_float2(o[d][2], o[d][3]);
+      }
+    }
+    __syncthreads();
+    if (wn == 1) return;
+    const float om_a = xm[ra], om_b = xm[rb];
+    const float nm_a = fmaxf(m_a, om_a), nm_b = fmaxf(m_b, om_b);
+    const float ua = nm_a == -INFINITY ? 0.f : nm_a, ub = nm_b == -INFINITY ? 0.f : nm_b;
+    const float sa = fast_exp2(m_a - ua), sb = fast_exp2(m_b - ub);     // scale of this warp's part
+    const float ta = fast_exp2(om_a - ua), tb = fast_exp2(om_b - ub);   // scale of the other's
+    l_a = l_a * sa + xl[ra] * ta;
+    l_b = l_b * sb + xl[rb] * tb;
+#pragma unroll
+    for (int d = 0; d < DH / 8; ++d) {
+      const float2 oa = *reinterpret_cast<const float2*>(xo + (size_t)ra * DH + d * 8 + 2 * t);
+      const float2 ob = *reinterpret_cast<const float2*>(xo + (size_t)rb * DH + d * 8 + 2 * t);
+      o[d][0] = o[d][0] * sa + oa.x * ta;
+      o[d][1] = o[d][1] * sa + oa.y * ta;
+      o[d][2] = o[d][2] * sb + ob.x * tb;
+      o[d][3] = o[d][3] * sb + ob.y * tb;
+    }
+  }
   const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
   if (ra < rows_valid) {
     bf16* op = p.out + ((size_t)(row0 + i0 + ra / group) * p.num_q_heads + m * group + ra % group) * DH;
@@ -1181,12 +1228,13 @@ static int blocks_resident(Kernel kernel, int threads, size_t smem, int* out) {
 #define SB_FN(name) SB_CONCAT(SB_CONCAT(name, _hd), SB_HEAD_DIM)
 
 // Ragged prefill attention.  items: [num_items, 2] (sequence, first token of a tile of
-// rows_per_tile / G tokens); rows_per_tile is 64 or 128.
+// rows_per_tile / G tokens); rows_per_tile is 64 or 128.  Tiles of 64 rows run with two key
+// groups (8 warps) unless single_key_group is set.
 extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const int* block_table, int max_pages,
                                       const int* cu_q, const int* q_start, void* out, int num_q_heads,
                                       int num_kv_heads, int page_size, int num_pages, float cap, int window,
-                                      const int* items, int num_items, int rows_per_tile, int* err,
-                                      cudaStream_t stream) {
+                                      const int* items, int num_items, int rows_per_tile, int single_key_group,
+                                      int* err, cudaStream_t stream) {
   if (num_items == 0) return 0;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > rows_per_tile) return -8;
   AttnParams p{};
@@ -1194,24 +1242,35 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.err = err;
+  // The merge of two key groups needs [BM][DH] floats where the tiles were.
+  constexpr bool split_fits = (size_t)(2 * 64 + 64 * DH) * sizeof(float) <= (size_t)4 * BN * PITCH * sizeof(bf16);
   if (rows_per_tile == 128) {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)prefill_smem(128));
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    sb_launch(attn_prefill_kernel<8>, dim3(num_items, num_kv_heads), 256, prefill_smem(128), stream, p);
-  } else if (rows_per_tile == 64) {
+    sb_launch(attn_prefill_kernel<8, 1>, dim3(num_items, num_kv_heads), 256, prefill_smem(128), stream, p);
+  } else if (rows_per_tile == 64 && split_fits && !single_key_group) {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)prefill_smem(64));
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    sb_launch(attn_prefill_kernel<4>, dim3(num_items, num_kv_heads), 128, prefill_smem(64), stream, p);
+    sb_launch(attn_prefill_kernel<4, 2>, dim3(num_items, num_kv_heads), 256, prefill_smem(64), stream, p);
+  } else if (rows_per_tile == 64) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)prefill_smem(64));
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    sb_launch(attn_prefill_kernel<4, 1>, dim3(num_items, num_kv_heads), 128, prefill_smem(64), stream, p);
   } else {
     return -8;
   }

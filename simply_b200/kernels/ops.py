@@ -90,8 +90,9 @@ class CudaOps:
     self.decode_chunk = 0
     # 0: the kernel is picked by the number of query rows; 1 forbids TMA; 16 forces the 16-row kernel (tests).
     self.decode_variant = 0
-    # 0: prefill tiles of 128 query rows when a sequence fills them, else 64; 64 or 128 forces one.
+    # 0: prefill tiles of 64 query rows; 64 or 128 forces a size.
     self.prefill_rows = 0
+    self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
     self.skinny_warps = 0
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
@@ -171,7 +172,7 @@ class CudaOps:
       c_int, c_float, c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
       prefill = getattr(lib, f"sb_attn_prefill_hd{head_dim}")
       prefill.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
-                          c_float, c_int, c_void, c_int, c_int, c_void, c_void]
+                          c_float, c_int, c_void, c_int, c_int, c_int, c_void, c_void]
       prefill.restype = c_int
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
@@ -252,8 +253,8 @@ class CudaOps:
     cu_q, q_start = ctx.host["cu_q"], ctx.host["q_start"].astype(np.int64)
     q_len = np.diff(cu_q).astype(np.int64)
     small = q_len * group <= 16
-    # Tiles of 128 query rows when a sequence fills them, else of 64.
-    rows_per_tile = self.prefill_rows or (128 if (q_len * group).max() >= 128 else 64)
+    # Tiles of 64 query rows (finer grains balance better over the SMs than tiles of 128).
+    rows_per_tile = self.prefill_rows or 64
     tokens_per_tile = rows_per_tile // group
     num_seqs = len(q_len)
     pre = []
@@ -443,7 +444,7 @@ class CudaOps:
       sizes = (num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window or 0))
       if plan["num_prefill"]:
         rc = prefill(*common, _ptr(out), *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
-                     plan["rows_per_tile"], _ptr(self.err), self._stream())
+                     plan["rows_per_tile"], int(self.prefill_single_key_group), _ptr(self.err), self._stream())
         self.launches += 1
         if rc:
           raise KernelError(f"sb_attn_prefill: {_STATUS.get(rc, rc)}")
