@@ -40,6 +40,8 @@ _STATUS = {
     -8: "query heads are no multiple of key/value heads",
     -9: "shape outside the weight-streaming product's range",
     -10: "batch outside the decode-advance kernel's range",
+    -11: "head size does not allow a tensor map",
+    -12: "the driver refused to encode a tensor map",
 }
 
 
@@ -120,6 +122,7 @@ class CudaOps:
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
+        "sb_gemm_tcgen05": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
     }
     for name, argtypes in protos.items():
@@ -326,6 +329,17 @@ class CudaOps:
       if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w), _ptr(out), m, n, k, 0, 0.0, 0, self.skinny_warps) == 0:
         return out
     return torch.mm(x, w.t())
+
+  def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, *, out_f32: bool = False, cap: float = 0.0,
+                     tile_n: int = 128) -> torch.Tensor | None:
+    """x [M, K] . w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate in tensor
+    memory); None when the shape is not taken (K not a multiple of 8)."""
+    m, k = x.shape
+    n = w.shape[0]
+    out = self._new(m, n, dtype=torch.float32 if out_f32 else torch.bfloat16)
+    rc = self._call("sb_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(out), m, n, k, int(out_f32), float(cap), tile_n,
+                    _ptr(self.err))
+    return out if rc == 0 else None
 
   def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, activation: int) -> torch.Tensor:
     """act(x . w_gate^T) * (x . w_up^T) with w_gate_up = [gate rows; up rows]: [M, N/2]."""

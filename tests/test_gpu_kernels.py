@@ -182,6 +182,21 @@ def test_linear_bfloat16(table, m, n, k):
   close(ops.linear(x.cuda(), w.cuda()), ref.linear(x, w), torch.bfloat16)
 
 
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 64, 128), (200, 1000, 2304), (2048, 2304, 2048), (64, 4096, 328),
+                                   (5, 70, 72)])
+def test_linear_tcgen05(table, tile_n, m, n, k):
+  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
+  x = torch.randn(m, k).to(torch.bfloat16)
+  w = (torch.randn(n, k) / k ** 0.5).to(torch.bfloat16)
+  got = ops.linear_tcgen05(x.cuda(), w.cuda(), tile_n=tile_n)
+  ops.check_errors()
+  close(got, ref.linear(x, w), torch.bfloat16)
+  got = ops.linear_tcgen05(x.cuda(), w.cuda(), out_f32=True, cap=3.0, tile_n=tile_n)
+  ops.check_errors()
+  torch.testing.assert_close(got.cpu(), ref.lm_head(x, w, 3.0), atol=2e-3, rtol=1e-3)
+
+
 @pytest.mark.parametrize("m", [1, 8, 13, 40])
 @pytest.mark.parametrize("f,k,act", [(160, 96, 0), (1000, 64, 1), (9216 // 4, 2304, 0)])
 def test_gated_linear(table, m, f, k, act):
