@@ -524,13 +524,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity; false after about a second without success.
+// Waits for the phase with the given parity; false after about half a second without success.
+__device__ __forceinline__ unsigned long long sb_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
-  for (int spin = 0; spin < (1 << 22); ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (spin > 64) __nanosleep(200);
+  // A try_wait may itself block for a while, so the bound is on time (half a second), not on tries.
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = sb_global_ns();
+  for (;;) {
+    for (int spin = 0; spin < 64; ++spin)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sb_global_ns() - start > 500000000ull) return false;
+    __nanosleep(100);
   }
-  return false;
 }
 // One box of the tensor map (columns [col, col + 64), rows [row, row + box rows)) to shared memory.
 __device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int col, int row, uint64_t* bar) {

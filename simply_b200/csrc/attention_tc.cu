@@ -1,0 +1,398 @@
+// Ragged paged prefill attention on the fifth-generation tensor cores (tcgen05), compiled once
+// per head size (-DSB_HEAD_DIM=N, N a multiple of 64 up to 256).
+//
+//   s = q . k                 (q is already rotated and scaled)
+//   s = cap * tanh(s / cap)   if cap > 0          simply/model_lib.py:621-626
+//   keep k_pos <= q_pos and, with a window W, q_pos - k_pos < W
+//                                                 simply/model_lib.py:469-515
+//   p = softmax(s) in float32, o = p . v          simply/model_lib.py:633-637
+//   query head n reads kv head n / G              simply/model_lib.py:2306-2310
+//
+// A block owns 128 query rows of one (sequence, kv head): the G query heads of the group for
+// 128 / G consecutive tokens.  It walks the keys in tiles of 64:
+//   S[128 x 64]  = Q . K^T     tcgen05.mma, accumulator in tensor memory (two S buffers)
+//   P            = softmax numerators of S, one thread per row (no shuffles), written to shared
+//                  memory as the next product's 128-row operand
+//   O[128 x DH] += P . V       tcgen05.mma, accumulator in tensor memory for the whole walk
+// Roles: warp 0 TMA producer (Q once; K/V tiles from the paged cache through the block table),
+// warp 1 MMA issue (one thread), warps 2..5 softmax and epilogue (a 32-lane quarter of tensor
+// memory each).  The running maximum is only moved when it grows by more than 8 (log2 units):
+// O is then rescaled in tensor memory; otherwise numerators up to 2^8 are kept, which float32
+// and bfloat16 hold without loss, and the final division by the row sum makes it exact.
+// All waits are bounded; a wait that runs out sets SB_ERR_TIMEOUT and the block leaves after
+// releasing its tensor memory.
+#include <float.h>
+
+#include "common.cuh"
+#include "tma_mbar.cuh"
+
+#ifndef SB_HEAD_DIM
+#define SB_HEAD_DIM 256
+#endif
+
+#if SB_HEAD_DIM % 64 == 0
+
+namespace {
+
+using namespace sbx;
+
+constexpr int DH = SB_HEAD_DIM;
+constexpr int BM = 128, BN = 64, SLABS = DH / 64;
+constexpr int Q_BYTES = BM * DH * 2, KV_TILE_BYTES = BN * DH * 2, P_BYTES = BM * BN * 2;
+constexpr int KV_STAGES = 2;
+constexpr int TC_THREADS = 192;
+constexpr int S_COL0 = 0, O_COL0 = 2 * BN;  // S buffers at columns 0 and 64, O from column 128
+constexpr int TMEM_COLS = O_COL0 + DH <= 256 ? 256 : 512;  // a power of two that holds S, S and O
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.f;
+
+struct TcParams {
+  const int* block_table;
+  int max_pages;
+  const int* cu_q;
+  const int* q_start;
+  bf16* out;
+  int num_q_heads, num_kv_heads, page_size, num_pages;
+  float cap;
+  int window;
+  const int* items;  // (sequence, first token of the tile of 128 / G tokens)
+  int box_rows;      // rows per key/value TMA box: min(page_size, 64)
+  int* err;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_q,
+                       const __grid_constant__ CUtensorMap map_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sq = base;                               // [SLABS][128 rows][128 B]
+  unsigned char* sk = sq + Q_BYTES;                       // [STAGES][SLABS][64 keys][128 B]
+  unsigned char* sv = sk + KV_STAGES * KV_TILE_BYTES;     // [STAGES][SLABS][64 keys][128 B]
+  unsigned char* sp = sv + KV_STAGES * KV_TILE_BYTES;     // [128 rows][128 B]
+  __shared__ __align__(8) uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], s_empty[2], p_ready,
+      pv_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_failed;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = p.items[2 * blockIdx.x], i0 = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
+  const int group = p.num_q_heads / p.num_kv_heads;
+  const int tokens_per_tile = BM / group;
+  const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
+  const int ntok = min(tokens_per_tile, q_len - i0);
+  const int rows_valid = ntok * group;
+  const int p0 = qs + i0, p1 = qs + i0 + ntok - 1;
+  const int kv_lo = p.window > 0 ? max(qs - p.window + 1, 0) : 0;  // lowest key the request still holds
+  const int lo = p.window > 0 ? max(p0 - p.window + 1, 0) : 0;     // lowest key this tile can see
+  const int kv_hi = p1 + 1;
+  const int tile0 = (lo / BN) * BN;
+  const int n_tiles = (kv_hi - tile0 + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+    }
+    mbar_init(&p_ready, 4);
+    mbar_init(&pv_done, 1);
+    s_failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 0) {
+    // ---- producer (one thread) -----------------------------------------------------------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&q_full, Q_BYTES);
+      for (int sl = 0; sl < SLABS; ++sl)  // box: 64 dims x G heads x 128 / G tokens, rows in (token, head) order
+        tma_load_3d(sq + sl * (BM * 128), &map_q, sl * 64, m * group, row0 + i0, &q_full);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % KV_STAGES;
+        if (j >= KV_STAGES && !mbar_wait_bounded(&kv_empty[s], (j / KV_STAGES - 1) & 1)) {
+          s_failed = 1;
+          break;
+        }
+        const int j0 = tile0 + j * BN;
+        int boxes = 0;
+        for (int r = 0; r < BN; r += p.box_rows) {
+          const int key = j0 + r;
+          if (key >= kv_hi || key + p.box_rows <= kv_lo) continue;
+          const long long page = p.block_table[(size_t)b * p.max_pages + key / p.page_size];
+          if (page >= 0 && page < p.num_pages) ++boxes;
+        }
+        mbar_arrive_expect_tx(&kv_full[s], boxes * 2 * SLABS * p.box_rows * 128);
+        for (int r = 0; r < BN; r += p.box_rows) {
+          const int key = j0 + r;
+          if (key >= kv_hi || key + p.box_rows <= kv_lo) continue;
+          const long long page = p.block_table[(size_t)b * p.max_pages + key / p.page_size];
+          if (page < 0 || page >= p.num_pages) {
+            atomicOr(p.err, SB_ERR_BAD_PAGE);
+            continue;
+          }
+          const long long krow = ((page * 2) * p.num_kv_heads + m) * p.page_size + (key & (p.page_size - 1));
+          const long long vrow = krow + (long long)p.num_kv_heads * p.page_size;
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_2d(sk + s * KV_TILE_BYTES + sl * (BN * 128) + r * 128, &map_kv, sl * 64, (int)krow, &kv_full[s]);
+            tma_load_2d(sv + s * KV_TILE_BYTES + sl * (BN * 128) + r * 128, &map_kv, sl * 64, (int)vrow, &kv_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue (one thread) -------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = idesc_bf16_f32(BM, BN, false, false);
+      const uint32_t idesc_pv = idesc_bf16_f32(BM, DH, false, true);  // V: the N index (dims) is contiguous
+      bool ok = mbar_wait_bounded(&q_full, 0);
+      auto issue_qk = [&](int j) {
+        const int s = j % KV_STAGES, sb = j & 1;
+        if (!mbar_wait_bounded(&kv_full[s], (j / KV_STAGES) & 1)) return false;
+        if (j >= 2 && !mbar_wait_bounded(&s_empty[sb], (j / 2 - 1) & 1)) return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < DH / 16; ++ks) {
+          const uint64_t a = smem_desc_sw128(sq + (ks / 4) * (BM * 128) + (ks % 4) * 32, 16, 1024);
+          const uint64_t bdesc = smem_desc_sw128(sk + s * KV_TILE_BYTES + (ks / 4) * (BN * 128) + (ks % 4) * 32, 16, 1024);
+          tc_mma_f16(tmem + S_COL0 + sb * BN, a, bdesc, idesc_qk, ks > 0);
+        }
+        tc_commit(&s_full[sb]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int s = j % KV_STAGES;
+        if (!mbar_wait_bounded(&p_ready, j & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t a = smem_desc_sw128(sp + kk * 32, 16, 1024);
+          // 16 keys further = 16 rows of 128 bytes; the next 64 dims are one slab (BN * 128 bytes) further
+          const uint64_t bdesc = smem_desc_sw128(sv + s * KV_TILE_BYTES + kk * 16 * 128, BN * 128, 1024);
+          tc_mma_f16(tmem + O_COL0, a, bdesc, idesc_pv, j > 0 || kk > 0);
+        }
+        tc_commit(&kv_empty[s]);
+        tc_commit(&pv_done);
+      }
+      if (!ok) s_failed = 1;
+    }
+  } else {
+    // ---- softmax and epilogue: one thread per query row ---------------------------------------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int pos = r < rows_valid ? p0 + r / group : -1;
+    // Positions of this warp's first and last row, for deciding whether a tile needs masking.
+    const bool rows_full = quarter * 32 + 31 < rows_valid;
+    const int warp_pos_lo = p0 + (quarter * 32) / group, warp_pos_hi = p0 + (quarter * 32 + 31) / group;
+    const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
+    float m_use = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1, s = j % KV_STAGES;
+      const int j0 = tile0 + j * BN;
+      if (!mbar_wait_bounded(&s_full[sb], (j / 2) & 1)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t sr[2][32];
+      tmem_load_32x32(tmem + lane_base + S_COL0 + sb * BN, sr[0]);
+      tmem_load_32x32(tmem + lane_base + S_COL0 + sb * BN + 32, sr[1]);
+      tmem_wait_load();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      const bool need_mask = !rows_full || j0 + BN - 1 > warp_pos_lo || (p.window > 0 && warp_pos_hi - j0 >= p.window);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float v = __uint_as_float(sr[h][c]);
+          if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
+          const int key = j0 + h * 32 + c;
+          const bool keep = !need_mask || (key <= pos && (p.window <= 0 || pos - key < p.window));
+          v = keep ? v * LOG2E : -INFINITY;
+          sr[h][c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      // Move the running maximum only when it grows by more than the threshold.
+      float alpha = 1.f;
+      if (mx > m_use + RESCALE_THRESHOLD || (m_use == -INFINITY && mx != -INFINITY)) {
+        alpha = fast_exp2(m_use - mx);  // 0 when there was no maximum yet
+        m_use = mx;
+      }
+      const float base_max = m_use == -INFINITY ? 0.f : m_use;
+      float sum = 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float e = fast_exp2(__uint_as_float(sr[h][c]) - base_max);
+          sum += e;
+          sr[h][c] = __float_as_uint(e);
+        }
+      l = l * alpha + sum;
+      // P's buffer and O are free once the last tile's P.V is done.
+      if (j > 0 && !mbar_wait_bounded(&pv_done, (j - 1) & 1)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < DH; c += 32) {
+          uint32_t o[32];
+          tmem_load_32x32(tmem + lane_base + O_COL0 + c, o);
+          tmem_wait_load();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_store_32x32(tmem + lane_base + O_COL0 + c, o);
+        }
+        tmem_wait_store();
+      }
+      // P as the 128-row operand of the next product: row r, 64 keys = 128 bytes, 16-byte chunks
+      // XOR-ed with the row's low three bits (the layout a 128-byte-swizzled TMA box would have).
+      unsigned char* prow = sp + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int h = c >> 2, o4 = (c & 3) * 8;
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(sr[h][o4 + 0]), __uint_as_float(sr[h][o4 + 1]));
+        v.y = pack_bf16(__uint_as_float(sr[h][o4 + 2]), __uint_as_float(sr[h][o4 + 3]));
+        v.z = pack_bf16(__uint_as_float(sr[h][o4 + 4]), __uint_as_float(sr[h][o4 + 5]));
+        v.w = pack_bf16(__uint_as_float(sr[h][o4 + 6]), __uint_as_float(sr[h][o4 + 7]));
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
+      }
+      // Value rows of keys that are not the request's must read as zeros (0 * garbage could be NaN):
+      // only in tiles that reach beyond [kv_lo, kv_hi).
+      if (j0 < kv_lo || j0 + BN > kv_hi) {
+        if (!mbar_wait_bounded(&kv_full[s], (j / KV_STAGES) & 1)) {
+          ok = false;
+          break;
+        }
+        for (int i = threadIdx.x - 64; i < BN * SLABS * 8; i += 128) {
+          const int key_row = (i / 8) % BN, sl = i / (8 * BN), c = i % 8;
+          const int key = j0 + key_row;
+          if (key < kv_lo || key >= kv_hi)
+            *reinterpret_cast<uint4*>(sv + s * KV_TILE_BYTES + sl * (BN * 128) + key_row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      fence_proxy_async();  // P (and zeroed value rows) are visible to the tensor core's reads
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready);
+    }
+    if (ok && n_tiles > 0 && !mbar_wait_bounded(&pv_done, (n_tiles - 1) & 1)) ok = false;
+    tc_fence_after_sync();
+    if (ok) {
+      // Every lane takes part in the warp-wide tensor-memory loads; only rows of the sequence store.
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const bool valid = r < rows_valid;
+      bf16* op = p.out + ((size_t)(row0 + i0 + (valid ? r / group : 0)) * p.num_q_heads + m * group + (valid ? r % group : 0)) * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t o[32];
+        tmem_load_32x32(tmem + lane_base + O_COL0 + c, o);
+        tmem_wait_load();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(op + c + i) = v;
+          }
+        }
+      }
+    }
+    if (!ok) s_failed = 1;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_failed) atomicOr(p.err, SB_ERR_TIMEOUT);
+  if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+constexpr size_t TC_SMEM = (size_t)Q_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + P_BYTES + 1024;
+
+}  // namespace
+
+#define SB_CONCAT2(a, b) a##b
+#define SB_CONCAT(a, b) SB_CONCAT2(a, b)
+#define SB_FN(name) SB_CONCAT(SB_CONCAT(name, _hd), SB_HEAD_DIM)
+
+// Ragged prefill attention on tcgen05.  q: [T, Hq, DH]; cache: [pages, 2, Hkv, page_size, DH];
+// items: [num_items, 2] (sequence, first token of a tile of 128 / G tokens).  Returns -11 when
+// the shapes do not allow it (the group must divide 128, the page size must be a power of two).
+extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                         const int* cu_q, const int* q_start, void* out, int num_tokens,
+                                         int num_q_heads, int num_kv_heads, int page_size, int num_pages, float cap,
+                                         int window, const int* items, int num_items, int* err, cudaStream_t stream) {
+  if (num_items == 0) return 0;
+  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
+  const int group = num_q_heads / num_kv_heads;
+  if (group > BM || BM % group || (page_size & (page_size - 1))) return -11;
+  SbEncodeTiled encode = sb_encode_tiled();
+  if (!encode) return -12;
+  CUtensorMap map_q, map_kv;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)DH, (cuuint64_t)num_q_heads, (cuuint64_t)num_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)DH * 2, (cuuint64_t)num_q_heads * DH * 2};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)group, (cuuint32_t)(BM / group)};
+    const cuuint32_t elem[3] = {1u, 1u, 1u};
+    if (encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return -12;
+  }
+  const int box_rows = page_size < BN ? page_size : BN;
+  if (sb_make_map_2d(&map_kv, cache, (long long)num_pages * 2 * num_kv_heads * page_size, DH, box_rows) != 0) return -12;
+  TcParams p{};
+  p.block_table = block_table; p.max_pages = max_pages; p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out;
+  p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
+  p.cap = cap; p.window = window; p.items = items; p.box_rows = box_rows; p.err = err;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  sb_launch(attn_prefill_tc_kernel, dim3(num_items, num_kv_heads), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+#endif  // head sizes that are no multiple of 64 do not get this kernel

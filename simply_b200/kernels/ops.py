@@ -94,6 +94,9 @@ class CudaOps:
     self.decode_variant = 0
     # 0: prefill tiles of 64 query rows; 64 or 128 forces a size.
     self.prefill_rows = 0
+    # Prefill attention on the tcgen05 tensor cores where the shapes allow (head size a multiple of
+    # 64, group dividing 128, page size a power of two); False keeps the mma.sync kernel.
+    self.prefill_tcgen05 = True
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
     self.skinny_warps = 0
@@ -185,7 +188,13 @@ class CudaOps:
       make_map = getattr(lib, f"sb_attn_tensor_map_hd{head_dim}")
       make_map.argtypes = [c_void, c_void, ctypes.c_longlong, c_int]
       make_map.restype = c_int
-      fns = self._attn_fns[head_dim] = (prefill, decode, make_map)
+      prefill_tc = None
+      if head_dim % 64 == 0:
+        prefill_tc = getattr(lib, f"sb_attn_prefill_tc_hd{head_dim}")
+        prefill_tc.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                               c_int, c_float, c_int, c_void, c_int, c_void, c_void]
+        prefill_tc.restype = c_int
+      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc)
     return fns
 
   def decode_chunk_for(self, batch: int, kv_len: int) -> int:
@@ -241,7 +250,7 @@ class CudaOps:
       self._tensor_maps[key] = buf
     return ctypes.c_void_p(buf[1]) if buf[1] is not None else None
 
-  def _attention_plan(self, ctx: Any, window: int | None, group: int) -> dict:
+  def _attention_plan(self, ctx: Any, window: int | None, group: int, force_rows: int = 0) -> dict:
     """Work lists of the two tensor-core kernels for this step, per (window, group).
 
     Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
@@ -257,7 +266,7 @@ class CudaOps:
     q_len = np.diff(cu_q).astype(np.int64)
     small = q_len * group <= 16
     # Tiles of 64 query rows (finer grains balance better over the SMs than tiles of 128).
-    rows_per_tile = self.prefill_rows or 64
+    rows_per_tile = force_rows or self.prefill_rows or 64
     tokens_per_tile = rows_per_tile // group
     num_seqs = len(q_len)
     pre = []
@@ -451,12 +460,20 @@ class CudaOps:
     out = self._new(t, num_heads * head_dim, dtype=q.dtype)
     group = num_heads // num_kv_heads
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
-      prefill, decode, _ = self._attention_lib(head_dim)
-      plan = self._attention_plan(ctx, window, group)
+      prefill, decode, _, prefill_tc = self._attention_lib(head_dim)
+      use_tc = (self.prefill_tcgen05 and prefill_tc is not None and 128 % group == 0
+                and ctx.page_size & (ctx.page_size - 1) == 0)
+      plan = self._attention_plan(ctx, window, group, 128 if use_tc else 0)
       common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
                 _ptr(ctx.q_start))
       sizes = (num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window or 0))
-      if plan["num_prefill"]:
+      if plan["num_prefill"] and use_tc:
+        rc = prefill_tc(*common, _ptr(out), t, *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
+                        _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_attn_prefill_tc: {_STATUS.get(rc, rc)}")
+      elif plan["num_prefill"]:
         rc = prefill(*common, _ptr(out), *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
                      plan["rows_per_tile"], int(self.prefill_single_key_group), _ptr(self.err), self._stream())
         self.launches += 1

@@ -303,14 +303,18 @@ def test_paged_attention_random(table, dtype, hq, hkv, dh, ps, window, cap):
                      device="cuda", ops=ops, seed=5)
   q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 1.5).to(dtype).cuda()
   want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)
-  # query rows per prefill tile; 65 stands for tiles of 64 rows with a single key group (4 warps)
-  for rows in ((0,) if dtype == torch.float32 else (0, 64, 65, 128)):
+  # Prefill kernels: tcgen05 where the shape allows; mma.sync with tiles of 64 rows (two key groups),
+  # 64 rows with a single key group (written 65 here) and 128 rows.
+  variants = [(False, 0)] if dtype == torch.float32 else [(True, 0), (False, 0), (False, 64), (False, 65), (False, 128)]
+  for tc, rows in variants:
+    ops.prefill_tcgen05 = tc
     ops.prefill_rows = (64 if rows == 65 else rows) if rows >= hq // hkv else 0
     ops.prefill_single_key_group = rows == 65
     sc.ctx.memo.clear()
     try:
       got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
     finally:
+      ops.prefill_tcgen05 = True
       ops.prefill_rows = 0
       ops.prefill_single_key_group = False
     ops.check_errors()
