@@ -11,12 +11,14 @@
 // A block owns 128 query rows of one (sequence, kv head): the G query heads of the group for
 // 128 / G consecutive tokens.  It walks the keys in tiles of 64:
 //   S[128 x 64]  = Q . K^T     tcgen05.mma, accumulator in tensor memory (two S buffers)
-//   P            = softmax numerators of S, one thread per row (no shuffles), written to shared
-//                  memory as the next product's 128-row operand
+//   P            = softmax numerators of S, written to shared memory as the next product's
+//                  128-row operand
 //   O[128 x DH] += P . V       tcgen05.mma, accumulator in tensor memory for the whole walk
-// Roles: warp 0 TMA producer (Q once; K/V tiles from the paged cache through the block table),
-// warp 1 MMA issue (one thread), warps 2..5 softmax and epilogue (a 32-lane quarter of tensor
-// memory each).  The running maximum is only moved when it grows by more than 8 (log2 units):
+// Roles: warp 0 TMA producer of Q (once) and of the key tiles, warp 2 of the value tiles (both
+// from the paged cache through the block table), warp 1 MMA issue (one thread), warps 4..19
+// softmax and epilogue: four threads per query row with 16 of the tile's 64 columns each (one
+// thread per row leaves each scheduler a single warp, and the instruction latency of the
+// softmax then bounds the tile).  The running maximum is only moved when it grows by more than 8 (log2 units):
 // O is then rescaled in tensor memory; otherwise numerators up to 2^8 are kept, which float32
 // and bfloat16 hold without loss, and the final division by the row sum makes it exact.
 // All waits are bounded; a wait that runs out sets SB_ERR_TIMEOUT and the block leaves after
@@ -40,7 +42,11 @@ constexpr int DH = SB_HEAD_DIM;
 constexpr int BM = 128, BN = 64, SLABS = DH / 64;
 constexpr int Q_BYTES = BM * DH * 2, KV_TILE_BYTES = BN * DH * 2, P_BYTES = BM * BN * 2;
 constexpr int KV_STAGES = 2;
-constexpr int TC_THREADS = 192;
+constexpr int SPLIT = 4;           // softmax threads per query row
+constexpr int CW = BN / SPLIT;     // columns of a key tile per softmax thread
+constexpr int OW = DH / SPLIT;     // columns of O per softmax thread (rescale, epilogue)
+static_assert(CW == 16 && OW % 16 == 0, "tensor-memory loads of 16 columns");
+constexpr int TC_THREADS = 128 + 128 * SPLIT;  // warps: key producer, MMA, value producer, spare, 4 * SPLIT softmax
 constexpr int S_COL0 = 0, O_COL0 = 2 * BN;  // S buffers at columns 0 and 64, O from column 128
 constexpr int TMEM_COLS = O_COL0 + DH <= 256 ? 256 : 512;  // a power of two that holds S, S and O
 constexpr float LOG2E = 1.4426950408889634f;
@@ -86,8 +92,9 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   unsigned char* sk = sq + Q_BYTES;                       // [STAGES][SLABS][64 keys][128 B]
   unsigned char* sv = sk + KV_STAGES * KV_TILE_BYTES;     // [STAGES][SLABS][64 keys][128 B]
   unsigned char* sp = sv + KV_STAGES * KV_TILE_BYTES;     // [128 rows][128 B]
-  __shared__ __align__(8) uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], s_empty[2], p_ready,
-      pv_done;
+  __shared__ __align__(8) uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES],
+      v_empty[KV_STAGES], s_full[2], s_empty[2], p_ready, pv_done, x_bar[4];
+  __shared__ float row_max[2][SPLIT][BM];  // the parts' row maxima of a tile (at the end: row sums)
   __shared__ uint32_t tmem_slot;
   __shared__ int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -107,14 +114,17 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+      mbar_init(&s_empty[s], 4 * SPLIT);
     }
-    mbar_init(&p_ready, 4);
+    for (int q = 0; q < 4; ++q) mbar_init(&x_bar[q], SPLIT);
+    mbar_init(&p_ready, 4 * SPLIT);
     mbar_init(&pv_done, 1);
     s_failed = 0;
     mbar_fence_init();
@@ -125,15 +135,23 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
 
-  if (warp == 0) {
-    // ---- producer (one thread) -----------------------------------------------------------------
+  if (warp == 0 || warp == 2) {
+    // ---- producers (one thread each): warp 0 brings Q and the key tiles, warp 2 the value tiles.
+    // Keys and values have rings of their own: a key tile is free as soon as its Q.K^T is done,
+    // long before the value tile of the same keys, so the next keys arrive early.
     if (lane == 0) {
-      mbar_arrive_expect_tx(&q_full, Q_BYTES);
-      for (int sl = 0; sl < SLABS; ++sl)  // box: 64 dims x G heads x 128 / G tokens, rows in (token, head) order
-        tma_load_3d(sq + sl * (BM * 128), &map_q, sl * 64, m * group, row0 + i0, &q_full);
+      const bool values = warp == 2;
+      uint64_t* full = values ? v_full : k_full;
+      uint64_t* empty = values ? v_empty : k_empty;
+      unsigned char* ring = values ? sv : sk;
+      if (!values) {
+        mbar_arrive_expect_tx(&q_full, Q_BYTES);
+        for (int sl = 0; sl < SLABS; ++sl)  // box: 64 dims x G heads x 128 / G tokens, rows in (token, head) order
+          tma_load_3d(sq + sl * (BM * 128), &map_q, sl * 64, m * group, row0 + i0, &q_full);
+      }
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % KV_STAGES;
-        if (j >= KV_STAGES && !mbar_wait_bounded(&kv_empty[s], (j / KV_STAGES - 1) & 1)) {
+        if (j >= KV_STAGES && !mbar_wait_bounded(&empty[s], (j / KV_STAGES - 1) & 1)) {
           s_failed = 1;
           break;
         }
@@ -145,7 +163,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           const long long page = p.block_table[(size_t)b * p.max_pages + key / p.page_size];
           if (page >= 0 && page < p.num_pages) ++boxes;
         }
-        mbar_arrive_expect_tx(&kv_full[s], boxes * 2 * SLABS * p.box_rows * 128);
+        mbar_arrive_expect_tx(&full[s], boxes * SLABS * p.box_rows * 128);
         for (int r = 0; r < BN; r += p.box_rows) {
           const int key = j0 + r;
           if (key >= kv_hi || key + p.box_rows <= kv_lo) continue;
@@ -154,12 +172,9 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
             atomicOr(p.err, SB_ERR_BAD_PAGE);
             continue;
           }
-          const long long krow = ((page * 2) * p.num_kv_heads + m) * p.page_size + (key & (p.page_size - 1));
-          const long long vrow = krow + (long long)p.num_kv_heads * p.page_size;
-          for (int sl = 0; sl < SLABS; ++sl) {
-            tma_load_2d(sk + s * KV_TILE_BYTES + sl * (BN * 128) + r * 128, &map_kv, sl * 64, (int)krow, &kv_full[s]);
-            tma_load_2d(sv + s * KV_TILE_BYTES + sl * (BN * 128) + r * 128, &map_kv, sl * 64, (int)vrow, &kv_full[s]);
-          }
+          const long long row = ((page * 2 + (values ? 1 : 0)) * p.num_kv_heads + m) * p.page_size + (key & (p.page_size - 1));
+          for (int sl = 0; sl < SLABS; ++sl)
+            tma_load_2d(ring + s * KV_TILE_BYTES + sl * (BN * 128) + r * 128, &map_kv, sl * 64, (int)row, &full[s]);
         }
       }
     }
@@ -171,7 +186,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       bool ok = mbar_wait_bounded(&q_full, 0);
       auto issue_qk = [&](int j) {
         const int s = j % KV_STAGES, sb = j & 1;
-        if (!mbar_wait_bounded(&kv_full[s], (j / KV_STAGES) & 1)) return false;
+        if (!mbar_wait_bounded(&k_full[s], (j / KV_STAGES) & 1)) return false;
         if (j >= 2 && !mbar_wait_bounded(&s_empty[sb], (j / 2 - 1) & 1)) return false;
         tc_fence_after_sync();
 #pragma unroll
@@ -181,6 +196,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           tc_mma_f16(tmem + S_COL0 + sb * BN, a, bdesc, idesc_qk, ks > 0);
         }
         tc_commit(&s_full[sb]);
+        tc_commit(&k_empty[s]);  // the key tile may be refilled once these MMAs have read it
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -188,7 +204,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
         const int s = j % KV_STAGES;
-        if (!mbar_wait_bounded(&p_ready, j & 1)) {
+        if (!mbar_wait_bounded(&p_ready, j & 1) || !mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
           ok = false;
           break;
         }
@@ -200,14 +216,17 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           const uint64_t bdesc = smem_desc_sw128(sv + s * KV_TILE_BYTES + kk * 16 * 128, BN * 128, 1024);
           tc_mma_f16(tmem + O_COL0, a, bdesc, idesc_pv, j > 0 || kk > 0);
         }
-        tc_commit(&kv_empty[s]);
+        tc_commit(&v_empty[s]);
         tc_commit(&pv_done);
       }
       if (!ok) s_failed = 1;
     }
-  } else {
-    // ---- softmax and epilogue: one thread per query row ---------------------------------------------
-    const int quarter = warp & 3;
+  } else if (warp >= 4) {
+    // ---- softmax and epilogue: SPLIT threads per query row, CW of the tile's 64 columns each ---------
+    // A warp may only touch the 32 lanes of tensor memory that (warp % 4) names, so the SPLIT
+    // threads of a row sit in the warps quarter, quarter + 4, ...  They agree on the row's
+    // maximum through shared memory once per tile; row sums stay partial until the end.
+    const int quarter = warp & 3, part = (warp - 4) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int pos = r < rows_valid ? p0 + r / group : -1;
@@ -215,6 +234,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     const bool rows_full = quarter * 32 + 31 < rows_valid;
     const int warp_pos_lo = p0 + (quarter * 32) / group, warp_pos_hi = p0 + (quarter * 32 + 31) / group;
     const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
+    const float scale2 = p.cap > 0.f ? p.cap * LOG2E : LOG2E;  // from x (tanh's value, or the score) to log2 units
     float m_use = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -225,44 +245,61 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         break;
       }
       tc_fence_after_sync();
-      uint32_t sr[2][32];
-      tmem_load_32x32(tmem + lane_base + S_COL0 + sb * BN, sr[0]);
-      tmem_load_32x32(tmem + lane_base + S_COL0 + sb * BN + 32, sr[1]);
+      uint32_t sr[CW];
+      tmem_load_32x16(tmem + lane_base + S_COL0 + sb * BN + part * CW, sr);
       tmem_wait_load();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       const bool need_mask = !rows_full || j0 + BN - 1 > warp_pos_lo || (p.window > 0 && warp_pos_hi - j0 >= p.window);
       float mx = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float v = __uint_as_float(sr[h][c]);
-          if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
-          const int key = j0 + h * 32 + c;
-          const bool keep = !need_mask || (key <= pos && (p.window <= 0 || pos - key < p.window));
-          v = keep ? v * LOG2E : -INFINITY;
-          sr[h][c] = __float_as_uint(v);
+        for (int c = 0; c < CW; ++c) {
+          float v = __uint_as_float(sr[c]);
+          if (p.cap > 0.f) v = fast_tanh(v * inv_cap);
+          const int key = j0 + part * CW + c;
+          v = (key <= pos && (p.window <= 0 || pos - key < p.window)) ? v : -INFINITY;
+          sr[c] = __float_as_uint(v);
           mx = fmaxf(mx, v);
         }
+      } else {
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+          float v = __uint_as_float(sr[c]);
+          if (p.cap > 0.f) v = fast_tanh(v * inv_cap);
+          sr[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      }
+      // The row's maximum over all parts.
+      row_max[j & 1][part][r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_bar[quarter]);
+      if (!mbar_wait_bounded(&x_bar[quarter], j & 1)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int q = 0; q < SPLIT; ++q) mx = fmaxf(mx, row_max[j & 1][q][r]);
+      mx *= scale2;
       // Move the running maximum only when it grows by more than the threshold.
       float alpha = 1.f;
       if (mx > m_use + RESCALE_THRESHOLD || (m_use == -INFINITY && mx != -INFINITY)) {
         alpha = fast_exp2(m_use - mx);  // 0 when there was no maximum yet
         m_use = mx;
       }
-      const float base_max = m_use == -INFINITY ? 0.f : m_use;
-      float sum = 0.f;
+      const float neg_base = m_use == -INFINITY ? 0.f : -m_use;
+      float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float e = fast_exp2(__uint_as_float(sr[h][c]) - base_max);
-          sum += e;
-          sr[h][c] = __float_as_uint(e);
-        }
-      l = l * alpha + sum;
+      for (int c = 0; c < CW; c += 2) {
+        const float e0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale2, neg_base));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale2, neg_base));
+        sum0 += e0;
+        sum1 += e1;
+        sr[c / 2] = pack_bf16(e0, e1);
+      }
+      l = l * alpha + (sum0 + sum1);
       // P's buffer and O are free once the last tile's P.V is done.
       if (j > 0 && !mbar_wait_bounded(&pv_done, (j - 1) & 1)) {
         ok = false;
@@ -271,13 +308,13 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       tc_fence_after_sync();
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-        for (int c = 0; c < DH; c += 32) {
-          uint32_t o[32];
-          tmem_load_32x32(tmem + lane_base + O_COL0 + c, o);
+        for (int c = part * OW; c < (part + 1) * OW; c += 16) {
+          uint32_t o[16];
+          tmem_load_32x16(tmem + lane_base + O_COL0 + c, o);
           tmem_wait_load();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_store_32x32(tmem + lane_base + O_COL0 + c, o);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_store_32x16(tmem + lane_base + O_COL0 + c, o);
         }
         tmem_wait_store();
       }
@@ -285,23 +322,18 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       // XOR-ed with the row's low three bits (the layout a 128-byte-swizzled TMA box would have).
       unsigned char* prow = sp + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int h = c >> 2, o4 = (c & 3) * 8;
-        uint4 v;
-        v.x = pack_bf16(__uint_as_float(sr[h][o4 + 0]), __uint_as_float(sr[h][o4 + 1]));
-        v.y = pack_bf16(__uint_as_float(sr[h][o4 + 2]), __uint_as_float(sr[h][o4 + 3]));
-        v.z = pack_bf16(__uint_as_float(sr[h][o4 + 4]), __uint_as_float(sr[h][o4 + 5]));
-        v.w = pack_bf16(__uint_as_float(sr[h][o4 + 6]), __uint_as_float(sr[h][o4 + 7]));
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
+      for (int c = 0; c < CW / 8; ++c) {
+        const int chunk = part * (CW / 8) + c;
+        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
       }
       // Value rows of keys that are not the request's must read as zeros (0 * garbage could be NaN):
       // only in tiles that reach beyond [kv_lo, kv_hi).
       if (j0 < kv_lo || j0 + BN > kv_hi) {
-        if (!mbar_wait_bounded(&kv_full[s], (j / KV_STAGES) & 1)) {
+        if (!mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
           ok = false;
           break;
         }
-        for (int i = threadIdx.x - 64; i < BN * SLABS * 8; i += 128) {
+        for (int i = threadIdx.x - 128; i < BN * SLABS * 8; i += 128 * SPLIT) {
           const int key_row = (i / 8) % BN, sl = i / (8 * BN), c = i % 8;
           const int key = j0 + key_row;
           if (key < kv_lo || key >= kv_hi)
@@ -313,6 +345,16 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
+    // The row's sum over all parts.
+    if (ok) {
+      row_max[n_tiles & 1][part][r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_bar[quarter]);
+      ok = mbar_wait_bounded(&x_bar[quarter], n_tiles & 1);
+      l = 0.f;
+#pragma unroll
+      for (int q = 0; q < SPLIT; ++q) l += row_max[n_tiles & 1][q][r];
+    }
     if (ok && n_tiles > 0 && !mbar_wait_bounded(&pv_done, (n_tiles - 1) & 1)) ok = false;
     tc_fence_after_sync();
     if (ok) {
@@ -321,13 +363,13 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       const bool valid = r < rows_valid;
       bf16* op = p.out + ((size_t)(row0 + i0 + (valid ? r / group : 0)) * p.num_q_heads + m * group + (valid ? r % group : 0)) * DH;
 #pragma unroll 1
-      for (int c = 0; c < DH; c += 32) {
-        uint32_t o[32];
-        tmem_load_32x32(tmem + lane_base + O_COL0 + c, o);
+      for (int c = part * OW; c < (part + 1) * OW; c += 16) {
+        uint32_t o[16];
+        tmem_load_32x16(tmem + lane_base + O_COL0 + c, o);
         tmem_wait_load();
         if (valid) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int i = 0; i < 16; i += 8) {
             uint4 v;
             v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
             v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
