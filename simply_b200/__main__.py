@@ -14,6 +14,7 @@ Token ids in, token ids out: one JSON object per prompt on standard output.
 from __future__ import annotations
 
 import json
+import os
 import sys
 
 from absl import app, flags
@@ -24,6 +25,9 @@ flags.DEFINE_string("ckpt_dir", None, "Model folder: config.json and *.safetenso
 flags.DEFINE_string("experiment_config", None,
                     "Name of a registered configuration (a preset); with --write_model_dir or "
                     "--random_weights it names the model to fill with random weights.")
+flags.DEFINE_string("config_overlay", None,
+                    "JSON object (or a file holding one) of config.json keys that replace the named "
+                    "configuration's values (simply/main.py:38-42).")
 flags.DEFINE_string("write_model_dir", None, "Write a random-weights model folder here and exit.")
 flags.DEFINE_bool("random_weights", False, "Run --experiment_config with random weights drawn on the GPU.")
 flags.DEFINE_integer("model_seed", 0, "Seed of the random weights.")
@@ -61,15 +65,29 @@ def _prompts() -> list[list[int]]:
   return prompts
 
 
+def _named_config():
+  from simply_b200.config import config_from_dict, preset, preset_dict
+  if not FLAGS.config_overlay:
+    return preset(FLAGS.experiment_config)
+  text = FLAGS.config_overlay
+  if os.path.exists(text):
+    with open(text) as f:
+      text = f.read()
+  overlay = json.loads(text)
+  if not isinstance(overlay, dict):
+    raise app.UsageError("--config_overlay must be a JSON object")
+  return config_from_dict({**preset_dict(FLAGS.experiment_config), **overlay})
+
+
 def main(argv):
   del argv
-  from simply_b200.config import EngineConfig, preset
+  from simply_b200.config import EngineConfig
   from simply_b200.weights import write_model_folder
 
   if FLAGS.write_model_dir:
     if not FLAGS.experiment_config:
       raise app.UsageError("--write_model_dir needs --experiment_config")
-    out = write_model_folder(preset(FLAGS.experiment_config), FLAGS.model_seed, FLAGS.write_model_dir,
+    out = write_model_folder(_named_config(), FLAGS.model_seed, FLAGS.write_model_dir,
                              matrix_std=FLAGS.matrix_std, scale_std=FLAGS.scale_std, dtype=FLAGS.weights_dtype)
     print(json.dumps({"wrote": out}))
     return 0
@@ -87,7 +105,7 @@ def main(argv):
   if FLAGS.ckpt_dir:
     engine = Engine.from_folder(FLAGS.ckpt_dir, ec)
   elif FLAGS.experiment_config and FLAGS.random_weights:
-    engine = Engine.from_config(preset(FLAGS.experiment_config), FLAGS.model_seed, ec,
+    engine = Engine.from_config(_named_config(), FLAGS.model_seed, ec,
                                 matrix_std=FLAGS.matrix_std, scale_std=FLAGS.scale_std)
   else:
     raise app.UsageError("give --ckpt_dir, or --experiment_config with --random_weights")
