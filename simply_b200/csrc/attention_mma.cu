@@ -886,7 +886,6 @@ __global__ void __launch_bounds__(WS_NT)
 attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, const __grid_constant__ CUtensorMap tmap,
                       int box_rows) {
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int TILE_ELEMS = D8_BN * DH;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* aligned = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -909,13 +908,19 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
-
+  // Launched early (programmatic dependent launch), the kernel before this one may still be
+  // writing the queries and the newest keys and values.  Everything else this kernel reads (work
+  // list, lengths, block table, older keys and values) is older than that kernel, so the producer
+  // fetches tiles of older keys at once and waits only before a tile that may hold new ones; the
+  // consumers wait before they read queries or write results.
   if (warp == D8_WARPS) {
     // ---- producer: one thread ------------------------------------------------------------
     if (lane != 0) return;
     unsigned seq = 0;  // tiles issued so far
+    bool waited = false;
     for (unsigned wi = 0;; ++wi) {
-      const int work = atomicAdd(work_counter, 1);
+      // The first item is the block's own index; further ones come from the counter.
+      const int work = wi == 0 ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(work_counter, 1);
       const int slot = wi % WS_RING;
       if (wi >= WS_RING && !mbar_wait_bounded(&work_empty[slot], (wi / WS_RING - 1) & 1)) {
         atomicOr(p.err, SB_ERR_TIMEOUT);
@@ -933,6 +938,10 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
           return;
         }
         const int j0 = w.begin + ti * D8_BN;
+        if (!waited && j0 + D8_BN > w.qs) {  // keys from position qs on are written by the step itself
+          pdl_wait();
+          waited = true;
+        }
         int boxes = 0;
         for (int r = 0; r < D8_BN; r += box_rows) {
           const int j = j0 + r;
@@ -977,6 +986,7 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
     if (!ws_item(p, work, w)) continue;
     const int rows_valid = w.q_len * group;  // <= 8 by the host's routing
     const size_t pidx = (size_t)(work / p.num_kv_heads) * p.num_kv_heads + w.m;
+    pdl_wait();  // before the first read of a query and the first write of a result
     if (w.n_tiles == 0) {
       // Nothing of this chunk is visible: an empty partial result.
       if (warp == 0) {
@@ -1154,21 +1164,22 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
                     bf16* __restrict__ out, int num_q_heads, int num_kv_heads, int rows_max,
                     int* __restrict__ work_counter) {
   pdl_launch_dependents();
-  pdl_wait();
-  // The split-key kernel has finished: put its work counter back to zero for the next launch.
-  if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
   __shared__ float s_acc[COMBINE_WARPS][DH];
   __shared__ float s_den[COMBINE_WARPS];
   __shared__ float s_max[COMBINE_WARPS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int tkn = blockIdx.x / num_q_heads, h = blockIdx.x - tkn * num_q_heads;
+  // The step's own lists are older than the split-key kernel: read them while it still runs.
   const int b = token_seq[tkn];
   const int count = split_count[b];
-  if (count <= 0) return;  // this sequence went through the prefill kernel
   const int group = num_q_heads / num_kv_heads, m = h / group;
   const int r = (tkn - cu_q[b]) * group + h % group;
   const size_t base = ((size_t)split_start[b] * num_kv_heads + m) * rows_max + r;
   const size_t stride = (size_t)num_kv_heads * rows_max;  // from one chunk's partial to the next
+  pdl_wait();
+  // The split-key kernel has finished: put its work counter back to zero for the next launch.
+  if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
+  if (count <= 0) return;  // this sequence went through the prefill kernel
   float mx = -INFINITY;
   for (int s = threadIdx.x; s < count; s += COMBINE_WARPS * 32) mx = fmaxf(mx, part_ml[(base + s * stride) * 2]);
   mx = warp_max(mx);
@@ -1324,7 +1335,7 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
     CUtensorMap map;
     memcpy(&map, tensor_map, sizeof(map));
     const int box_rows = page_size < D8_BN ? page_size : D8_BN;
-    sb_launch(attn_decode8ws_kernel, total_work < resident_ws ? total_work : resident_ws, WS_NT, smem, stream,
+    sb_launch_early(attn_decode8ws_kernel, total_work < resident_ws ? total_work : resident_ws, WS_NT, smem, stream,
         p, work_counter, total_work, map, box_rows);
   } else if (rows_max <= 8 && variant != 16 && TMA_OK && tensor_map != nullptr && power_of_two_pages && variant != 1) {
     static int resident_tma = 0;
@@ -1358,11 +1369,27 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
         p, work_counter, total_work);
   }
   SB_LAUNCH_CHECK();
-  sb_launch(attn_combine_kernel, (unsigned)(num_tokens * num_q_heads), COMBINE_WARPS * 32, 0, stream,
+  sb_launch_early(attn_combine_kernel, (unsigned)(num_tokens * num_q_heads), COMBINE_WARPS * 32, 0, stream,
       part_o, part_ml, token_seq, cu_q, split_start, split_count, (bf16*)out, num_q_heads, num_kv_heads,
       rows_max, work_counter);
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+// How many blocks of the split-key kernel for at most 8 query rows the device holds at once (the
+// size of its persistent grid): the host cuts the keys into chunks so that the work items fill
+// this many blocks evenly.  Returns the count, or a negative status.
+extern "C" int SB_FN(sb_attn_decode_resident)(int with_tensor_map) {
+  int resident = 0, rc;
+  constexpr size_t ws_merge = (size_t)(D8_WARPS * 8 * DH) * sizeof(float);
+  constexpr bool ws_fits = ws_merge <= (size_t)D8_BN * DH * sizeof(bf16);
+  if (with_tensor_map && TMA_OK && ws_fits) {
+    constexpr size_t smem = (size_t)(2 * WS_STAGES * D8_BN) * DH * sizeof(bf16) + 1024;
+    rc = blocks_resident(attn_decode8ws_kernel, WS_NT, smem, &resident);
+  } else {
+    rc = blocks_resident(attn_decode8_kernel<false>, D8_NT, DECODE8_SMEM, &resident);
+  }
+  return rc ? (rc > 0 ? -rc : rc) : resident;
 }
 
 // Writes into `map_out` (128 bytes, host memory) the tensor map of one cache storage

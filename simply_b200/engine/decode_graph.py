@@ -47,7 +47,7 @@ class _Graph:
   captured: bool
   batch: int
   bucket: int
-  chunk: int
+  chunks: dict
   launches: int
 
 
@@ -59,13 +59,21 @@ class DecodeRunner:
     self.engine = engine
     self.ops = engine.ops
     self.graphs: dict[tuple[int, int], _Graph] = {}
-    self.attn_kinds = sorted(
-        {(b.mixer.window, b.mixer.num_heads // b.mixer.num_kv_heads) for b in engine.model.blocks.values()},
-        key=lambda k: (k[0] or 0, k[1]))
+    # Kinds of attention by (window, group), each with the kv heads and head size of its first layer.
+    kinds: dict[tuple, tuple[int, int]] = {}
+    for b in engine.model.blocks.values():
+      kinds.setdefault((b.mixer.window, b.mixer.num_heads // b.mixer.num_kv_heads),
+                       (b.mixer.num_kv_heads, b.mixer.head_dim))
+    self.attn_kinds = sorted(kinds, key=lambda k: (k[0] or 0, k[1]))
+    self.attn_shapes = kinds
     self.stream = torch.cuda.Stream(device=engine.device)
 
   # ---- layout of the static buffer -----------------------------------------------
-  def _layout(self, batch: int, bucket: int, chunk: int) -> tuple[dict, dict, int]:
+  def _span(self, bucket: int, window: int | None) -> int:
+    """Most keys a sequence of this bucket sees in a layer with this window during a burst."""
+    return min(bucket, window + self.MAX_BURST + 64) if window else bucket
+
+  def _layout(self, batch: int, bucket: int, chunks: dict) -> tuple[dict, dict, int]:
     cache = self.engine.cache
     views, off = {}, 0
 
@@ -83,8 +91,7 @@ class DecodeRunner:
       take(f"table{gi}", batch * g.max_pages_per_seq)
     items_per_seq = {}
     for window, group in self.attn_kinds:
-      span = min(bucket, window + self.MAX_BURST + 64) if window else bucket
-      per_seq = -(-span // chunk) + 1
+      per_seq = -(-self._span(bucket, window) // chunks[(window, group)]) + 1
       items_per_seq[(window, group)] = per_seq
       take(f"items{window}_{group}", batch * per_seq * 2)
       take(f"split_start{window}_{group}", batch)
@@ -94,8 +101,12 @@ class DecodeRunner:
   def _prepare(self, batch: int, bucket: int) -> _Graph:
     """Static buffers and the step closure for one (batch, bucket); nothing runs yet."""
     eng, ops = self.engine, self.ops
-    chunk = ops.decode_chunk_for(batch, bucket)
-    views, items_per_seq, words = self._layout(batch, bucket, chunk)
+    chunks = {}
+    for window, group in self.attn_kinds:
+      span = self._span(bucket, window)
+      chunks[(window, group)] = ops.decode_chunk_for([bucket - span] * batch, [bucket] * batch,
+                                                     *self.attn_shapes[(window, group)])
+    views, items_per_seq, words = self._layout(batch, bucket, chunks)
     meta = torch.zeros(words, dtype=torch.int32, device=eng.device)
     host = torch.zeros(words, dtype=torch.int32).pin_memory()
 
@@ -113,7 +124,8 @@ class DecodeRunner:
     plans = {}
     for (window, group), per_seq in items_per_seq.items():
       plans[(window, group)] = dict(
-          num_prefill=0, num_decode=batch * per_seq, chunk=chunk, rows_max=group, rows_per_tile=64,
+          num_prefill=0, num_decode=batch * per_seq, chunk=chunks[(window, group)], rows_max=group,
+          rows_per_tile=64,
           prefill_items=None, decode_items=view(f"items{window}_{group}"),
           split_start=view(f"split_start{window}_{group}"), split_count=view(f"split_count{window}_{group}"))
     sampled = torch.zeros(batch, dtype=torch.int32, device=eng.device)
@@ -128,7 +140,7 @@ class DecodeRunner:
                          view("sample_params"), history, view("step_counter"))
 
     g = _Graph(torch.cuda.CUDAGraph(), meta, host, views, plans, sampled, history, host_history, one_step,
-               False, batch, bucket, chunk, 0)
+               False, batch, bucket, chunks, 0)
     self._fill_constants(g)
     return g
 
@@ -199,7 +211,7 @@ class DecodeRunner:
       put(f"table{gi}", grp.tables[np.asarray(slots)])
     for (window, group), plan in g.plans.items():
       per_seq = plan["num_decode"] // batch
-      items, start, count = self.ops.static_decode_plan(lengths, steps, window, g.chunk, per_seq)
+      items, start, count = self.ops.static_decode_plan(lengths, steps, window, plan["chunk"], per_seq)
       put(f"items{window}_{group}", items)
       put(f"split_start{window}_{group}", start)
       put(f"split_count{window}_{group}", count)

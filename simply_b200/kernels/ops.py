@@ -16,7 +16,7 @@ norms, rotation, cache write, activation, embedding, sampling) is hand-written.
 from __future__ import annotations
 
 import ctypes
-from typing import Any
+from typing import Any, Sequence
 
 import numpy as np
 import torch
@@ -86,10 +86,10 @@ class CudaOps:
     self._attn_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
     # bfloat16 attention runs on tensor cores where the shape allows; False forces the general kernel.
     self.tensor_core_attention = True
-    # Split-key attention: about this many (sequence, chunk) items per kv head are aimed for;
-    # decode_chunk > 0 fixes the chunk length instead (a multiple of 64).
-    self.decode_target_items = 148 * 2
+    # Split-key attention: the chunk length is chosen so that the work items fill the kernel's
+    # persistent grid evenly; decode_chunk > 0 fixes it instead (a multiple of 64).
     self.decode_chunk = 0
+    self._decode_slots: dict[int, int] = {}
     # 0: the kernel is picked by the number of query rows; 1 forbids TMA; 16 forces the 16-row kernel (tests).
     self.decode_variant = 0
     # 0: prefill tiles of 64 query rows; 64 or 128 forces a size.
@@ -194,19 +194,40 @@ class CudaOps:
         prefill_tc.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                c_int, c_float, c_int, c_void, c_int, c_void, c_void]
         prefill_tc.restype = c_int
+      resident = getattr(lib, f"sb_attn_decode_resident_hd{head_dim}")
+      resident.argtypes, resident.restype = [c_int], c_int
+      slots = resident(1)
+      if slots <= 0:
+        raise KernelError(f"sb_attn_decode_resident: {_STATUS.get(slots, slots)}")
+      self._decode_slots[head_dim] = slots
       fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc)
     return fns
 
-  def decode_chunk_for(self, batch: int, kv_len: int) -> int:
-    """Chunk length of split-key attention for `batch` sequences of up to `kv_len` keys."""
+  def decode_chunk_for(self, kv_lo: Sequence[int], kv_hi: Sequence[int], num_kv_heads: int, head_dim: int) -> int:
+    """Chunk length of split-key attention for sequences that see the keys [kv_lo, kv_hi).
+
+    A work item is one chunk of one (sequence, kv head); the kernel's persistent grid draws items
+    from a counter.  With `slots` resident blocks the launch lasts about
+    ceil(items / slots) * (chunk + fixed cost of an item), so the chunk is the multiple of 64 that
+    makes this smallest: the items then fill the grid in whole rounds instead of leaving most
+    blocks idle in the last one.
+    """
     if self.decode_chunk:
       return self.decode_chunk
-    return self._chunk_for_keys(batch * kv_len)
+    self._attention_lib(head_dim)
+    slots = self._decode_slots[head_dim]
+    lo, hi = np.asarray(kv_lo, dtype=np.int64), np.asarray(kv_hi, dtype=np.int64)
+    best, best_cost = 64, None
+    for chunk in range(64, 2048 + 1, 64):
+      items = int(((hi - 1) // chunk - lo // chunk + 1).sum()) * num_kv_heads
+      cost = -(-items // slots) * (chunk + self.DECODE_ITEM_COST)
+      if best_cost is None or cost <= best_cost:
+        best, best_cost = chunk, cost
+    return best
 
-  def _chunk_for_keys(self, total_keys: int) -> int:
-    # Chunks are drawn dynamically by a persistent grid, so they only need to be small enough
-    # to balance and large enough to amortise a block's start: 128 to 512 keys.
-    return int(min(max(-(-total_keys // self.decode_target_items) + 63 >> 6 << 6, 128), 512))
+  # Fixed cost of a split-key work item (pipeline fill, partial result, its share of the merge),
+  # in keys: about 2 microseconds of a block's share of the memory bandwidth.
+  DECODE_ITEM_COST = 48
 
   @staticmethod
   def static_decode_plan(q_start: np.ndarray, steps: int, window: int | None, chunk: int,
@@ -250,7 +271,8 @@ class CudaOps:
       self._tensor_maps[key] = buf
     return ctypes.c_void_p(buf[1]) if buf[1] is not None else None
 
-  def _attention_plan(self, ctx: Any, window: int | None, group: int, force_rows: int = 0) -> dict:
+  def _attention_plan(self, ctx: Any, window: int | None, group: int, force_rows: int = 0,
+                      num_kv_heads: int = 1, head_dim: int = 0) -> dict:
     """Work lists of the two tensor-core kernels for this step, per (window, group).
 
     Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
@@ -283,8 +305,7 @@ class CudaOps:
     dec = np.nonzero(small)[0]
     chunk = 64
     if len(dec):
-      total = int((kv_hi[dec] - kv_lo[dec]).sum())
-      chunk = self.decode_chunk or self._chunk_for_keys(total)
+      chunk = self.decode_chunk_for(kv_lo[dec], kv_hi[dec], num_kv_heads, head_dim)
     split_start = np.zeros(num_seqs, dtype=np.int32)
     split_count = np.zeros(num_seqs, dtype=np.int32)
     dec_items = []
@@ -463,7 +484,7 @@ class CudaOps:
       prefill, decode, _, prefill_tc = self._attention_lib(head_dim)
       use_tc = (self.prefill_tcgen05 and prefill_tc is not None and 128 % group == 0
                 and ctx.page_size & (ctx.page_size - 1) == 0)
-      plan = self._attention_plan(ctx, window, group, 128 if use_tc else 0)
+      plan = self._attention_plan(ctx, window, group, 128 if use_tc else 0, num_kv_heads, head_dim)
       common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
                 _ptr(ctx.q_start))
       sizes = (num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window or 0))
