@@ -71,6 +71,8 @@ class PageGroup:
   def apply(self, slot: int, cur_len: int, n_new: int) -> tuple[list[int], list[int]]:
     """Carries out `plan`; returns (pages given back, pages taken)."""
     n_back, n_take = self.plan(slot, cur_len, n_new)
+    if n_back == 0 and n_take == 0:
+      return [], []  # the usual decode step: the token lands in a page the slot already holds
     first, end = int(self.first_page[slot]), int(self.end_page[slot])
     row = self.tables[slot]
     back = [int(p) for p in row[first:first + n_back]]

@@ -137,7 +137,15 @@ class Scheduler:
       return lo
 
     # 1. Decoding requests, oldest first.  Each must run; make room if needed.
-    for r in sorted((r for r in self.running if r.is_decoding), key=lambda r: r.arrival):
+    decoding = sorted((r for r in self.running if r.is_decoding), key=lambda r: r.arrival)
+    if decoding and len(decoding) <= budget and self.cache.pages_short([(r.slot, 1) for r in decoding]) == 0:
+      # The usual case, decided with one look at the pools: all of them fit, so each prefix does.
+      for r in decoding:
+        chosen.append((r.slot, 1))
+        plan.entries.append(PlannedEntry(r, 1, True))
+      budget -= len(decoding)
+      decoding = []
+    for r in decoding:
       if r.status is not Status.RUNNING:
         continue  # preempted below while making room for an older one
       if budget == 0:
