@@ -1153,8 +1153,8 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
 }
 
 // Merges the chunks of every (token, query head): one block each.  Its warps take the
-// chunks in turn (warp w: chunks w, w + 4, ...), then add up in a fixed order.
-constexpr int COMBINE_WARPS = 4;
+// chunks in turn (warp w: chunks w, w + 8, ...), then add up in a fixed order.
+constexpr int COMBINE_WARPS = 8;
 constexpr int DPL = (DH + 31) / 32;  // output elements per lane
 
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
@@ -1180,26 +1180,30 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   // The split-key kernel has finished: put its work counter back to zero for the next launch.
   if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
   if (count <= 0) return;  // this sequence went through the prefill kernel
-  float mx = -INFINITY;
-  for (int s = threadIdx.x; s < count; s += COMBINE_WARPS * 32) mx = fmaxf(mx, part_ml[(base + s * stride) * 2]);
-  mx = warp_max(mx);
-  if (lane == 0) s_max[warp] = mx;
-  __syncthreads();
-  mx = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+  // One pass: every warp merges its share of the chunks with a running maximum (the loads of a
+  // few chunks are in flight together), then the warps' results are merged through shared memory.
+  float m_run = -INFINITY, den = 0.f;
   float acc[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-  float den = 0.f;
 #pragma unroll 4
   for (int s = warp; s < count; s += COMBINE_WARPS) {
     const size_t pidx = base + s * stride;
     const float ms = part_ml[pidx * 2], ls = part_ml[pidx * 2 + 1];
-    const float w = ls > 0.f ? ls * fast_exp2(ms - mx) : 0.f;  // an empty chunk stored zeros
-    den += w;
+    float o[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int d = lane + 32 * i;
-      if (d < DH) acc[i] = fmaf(w, part_o[pidx * DH + d], acc[i]);
+      o[i] = d < DH ? part_o[pidx * DH + d] : 0.f;
+    }
+    if (ls > 0.f) {  // an empty chunk stored zeros
+      const float m_new = fmaxf(m_run, ms);
+      const float keep = fast_exp2(m_run - m_new);  // 0 for the first chunk
+      const float w = ls * fast_exp2(ms - m_new);
+      den = den * keep + w;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[i] = fmaf(w, o[i], acc[i] * keep);
+      m_run = m_new;
     }
   }
 #pragma unroll
@@ -1207,13 +1211,29 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     const int d = lane + 32 * i;
     if (d < DH) s_acc[warp][d] = acc[i];
   }
-  if (lane == 0) s_den[warp] = den;
+  if (lane == 0) {
+    s_den[warp] = den;
+    s_max[warp] = m_run;
+  }
   __syncthreads();
-  den = (s_den[0] + s_den[1]) + (s_den[2] + s_den[3]);
+  float mx = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < COMBINE_WARPS; ++w) mx = fmaxf(mx, s_max[w]);
+  float scale[COMBINE_WARPS];
+  den = 0.f;
+#pragma unroll
+  for (int w = 0; w < COMBINE_WARPS; ++w) {
+    scale[w] = s_max[w] == -INFINITY ? 0.f : fast_exp2(s_max[w] - mx);
+    den += s_den[w] * scale[w];
+  }
   const float inv = den > 0.f ? 1.0f / den : 0.f;
   bf16* op = out + ((size_t)tkn * num_q_heads + h) * DH;
-  for (int d = threadIdx.x; d < DH; d += COMBINE_WARPS * 32)
-    op[d] = __float2bfloat16_rn(((s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d])) * inv);
+  for (int d = threadIdx.x; d < DH; d += COMBINE_WARPS * 32) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < COMBINE_WARPS; ++w) v = fmaf(s_acc[w][d], scale[w], v);
+    op[d] = __float2bfloat16_rn(v * inv);
+  }
 }
 
 constexpr size_t prefill_smem(int rows) { return (size_t)(rows + 4 * BN) * PITCH * sizeof(bf16); }
