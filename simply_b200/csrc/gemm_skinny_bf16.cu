@@ -14,8 +14,26 @@
 // Epilogues: 0 store as bfloat16; 1 store float32 with an optional soft cap
 // (simply/model_lib.py:107-109, the output layer); 2 gated activation: the block
 // also owns rows [N/2 + n0, N/2 + n0 + 16) and stores act(gate) * up
-// (simply/model_lib.py:722-726).
+// (simply/model_lib.py:722-726); 3 the fused q, k, v projection of an attention layer: a block
+// owns 16 dims of a head and the 16 dims half a head further, rotates the pairs
+// (simply/utils/position_encoding.py:83-110), scales the query (simply/model_lib.py:2014-2019)
+// and stores queries to their buffer, keys and values into the pages of the cache.
 #include "common.cuh"
+
+// What epilogue 3 needs besides the product.  cos_t / sin_t: [M, head_dim / 2] float32 or null.
+struct RopeStore {
+  const float* cos_t;
+  const float* sin_t;
+  float q_scale;
+  bf16* q_out;   // [M, num_q_heads, head_dim]
+  bf16* cache;   // [pages, 2, num_kv_proj, page_size, head_dim] or null
+  const int* block_table;
+  int max_pages;
+  const int* token_seq;
+  const int* positions;
+  int num_q_heads, num_kv_proj, head_dim, page_size, num_pages;
+  int* err;
+};
 
 __device__ __forceinline__ float skinny_activation(float g, int act) {
   if (act == 0) {
@@ -43,20 +61,26 @@ __device__ __forceinline__ uint4 load_stream16(const bf16* p) {
 template <int MT, int WARPS, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void* __restrict__ out, int M,
-                   int N, int K, float cap, int act) {
+                   int N, int K, float cap, int act, const RopeStore rs) {
   pdl_launch_dependents();
-  constexpr int SETS = EPI == 2 ? 2 : 1;
+  constexpr int SETS = EPI >= 2 ? 2 : 1;
   __shared__ float partial[WARPS][SETS][MT][16][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n_out = EPI == 2 ? N / 2 : N;  // rows a block set ranges over
-  const int n0 = blockIdx.x * 16;
+  // Epilogue 3: block (head, slice) owns rows head * head_dim + 16 * slice + [0, 16) and the rows
+  // half a head further; the others: rows 16 * block + [0, 16) (and those N / 2 further).
+  const int half = EPI == 3 ? rs.head_dim / 2 : 0;
+  const int slices = EPI == 3 ? half / 16 : 1;
+  const int head = EPI == 3 ? blockIdx.x / slices : 0;
+  const int n0 = EPI == 3 ? head * rs.head_dim + (blockIdx.x - head * slices) * 16 : blockIdx.x * 16;
+  const int set_stride = EPI == 3 ? half : n_out;
   // Rows past the end are clamped for loading and dropped when storing.
   const bf16* wr[SETS][2];
 #pragma unroll
   for (int s = 0; s < SETS; ++s) {
-    wr[s][0] = w + (size_t)(s * n_out + min(n0 + g, n_out - 1)) * K;
-    wr[s][1] = w + (size_t)(s * n_out + min(n0 + g + 8, n_out - 1)) * K;
+    wr[s][0] = w + (size_t)min(s * set_stride + n0 + g, N - 1) * K;
+    wr[s][1] = w + (size_t)min(s * set_stride + n0 + g + 8, N - 1) * K;
   }
   const bf16* xr[MT];
   bool xok[MT];
@@ -151,7 +175,38 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
       v[s] = sum;
     }
     const size_t o = (size_t)token * n_out + n;
-    if (EPI == 0) {
+    if (EPI == 3) {
+      // Round to bfloat16 first, as the unfused path stores the projection before it rotates.
+      float a = __bfloat162float(__float2bfloat16_rn(v[0]));
+      float b = __bfloat162float(__float2bfloat16_rn(v[SETS - 1]));
+      const int j = n - head * rs.head_dim;  // the dim inside the head, below half
+      if (head < rs.num_q_heads + rs.num_kv_proj && rs.cos_t != nullptr) {
+        const float c = rs.cos_t[(size_t)token * half + j], sn = rs.sin_t[(size_t)token * half + j];
+        const float ra = a * c - b * sn, rb = b * c + a * sn;
+        a = ra;
+        b = rb;
+      }
+      bf16* dst = nullptr;
+      if (head < rs.num_q_heads) {
+        a *= rs.q_scale;
+        b *= rs.q_scale;
+        dst = rs.q_out + ((size_t)token * rs.num_q_heads + head) * rs.head_dim;
+      } else if (rs.cache != nullptr) {
+        const int pos = rs.positions[token];
+        const long long page = rs.block_table[(size_t)rs.token_seq[token] * rs.max_pages + pos / rs.page_size];
+        if (page < 0 || page >= rs.num_pages) {
+          atomicOr(rs.err, SB_ERR_BAD_PAGE);
+        } else {
+          const int kv = head < rs.num_q_heads + rs.num_kv_proj ? 0 : 1;
+          const int m = head - rs.num_q_heads - kv * rs.num_kv_proj;
+          dst = rs.cache + ((((size_t)page * 2 + kv) * rs.num_kv_proj + m) * rs.page_size + pos % rs.page_size) * rs.head_dim;
+        }
+      }
+      if (dst != nullptr) {
+        dst[j] = __float2bfloat16_rn(a);
+        dst[j + half] = __float2bfloat16_rn(b);
+      }
+    } else if (EPI == 0) {
       reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v[0]);
     } else if (EPI == 1) {
       reinterpret_cast<float*>(out)[o] = cap > 0.f ? cap * tanhf(v[0] / cap) : v[0];
@@ -166,18 +221,21 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
 
 template <int MT, int WARPS>
 static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, int K, int epilogue, float cap,
-                         int act, cudaStream_t stream) {
+                         int act, cudaStream_t stream, const RopeStore& rs = RopeStore{}) {
   const int n_out = epilogue == 2 ? N / 2 : N;
-  const unsigned blocks = (unsigned)((n_out + 15) / 16);
+  const unsigned blocks = epilogue == 3 ? (unsigned)(N / 32) : (unsigned)((n_out + 15) / 16);
   if (epilogue == 0)
     sb_launch_early(skinny_gemm_kernel<MT, WARPS, 0>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
-        act);
+        act, rs);
   else if (epilogue == 1)
     sb_launch_early(skinny_gemm_kernel<MT, WARPS, 1>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
-        act);
-  else
+        act, rs);
+  else if (epilogue == 2)
     sb_launch_early(skinny_gemm_kernel<MT, WARPS, 2>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
-        act);
+        act, rs);
+  else
+    sb_launch_early(skinny_gemm_kernel<MT, WARPS, 3>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
+        act, rs);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -213,4 +271,36 @@ extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int 
   // (8 warps at most: with 16 the partial sums of the gated epilogue outgrow static shared memory.)
   if (warps == 4) return launch_skinny<4, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
   return launch_skinny<4, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+}
+
+// The fused q, k, v projection of an attention layer for at most 16 tokens: product, rotation,
+// query scale, and the stores of queries (q_out) and of keys and values (pages of `cache`).
+// w: [(num_q_heads + 2 * num_kv_proj) * head_dim, K], heads in the order q, k, v.
+// cos_t / sin_t null: no rotation; cache null: keys and values are not stored.
+// Returns -9 for shapes it does not take (M > 16, K % 8 != 0, head_dim % 32 != 0).
+extern "C" int sb_qkv_rope_skinny(const void* x, const void* w, int M, int K, const float* cos_t,
+                                  const float* sin_t, float q_scale, void* q_out, void* cache,
+                                  const int* block_table, int max_pages, const int* token_seq,
+                                  const int* positions, int num_q_heads, int num_kv_proj, int head_dim,
+                                  int page_size, int num_pages, int* err, int warps_override,
+                                  cudaStream_t stream) {
+  if (M == 0) return 0;
+  if (M > 16 || K % 8 != 0 || K <= 0 || head_dim <= 0 || head_dim % 32 != 0 || num_q_heads <= 0) return -9;
+  RopeStore rs{cos_t, sin_t, q_scale, (bf16*)q_out, (bf16*)cache, block_table, max_pages, token_seq, positions,
+               num_q_heads, num_kv_proj, head_dim, page_size, num_pages, err};
+  const int N = (num_q_heads + 2 * num_kv_proj) * head_dim;
+  const int blocks = N / 32;
+  int warps = blocks <= 148 ? 16 : blocks <= 296 ? 8 : 4;
+  if (K < warps * 32 * 2) warps = K >= 8 * 32 * 2 ? 8 : 4;
+  if (warps_override == 4 || warps_override == 8 || warps_override == 16) warps = warps_override;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)w;
+  if (M <= 8) {
+    if (warps == 16) return launch_skinny<1, 16>(xp, wp, nullptr, M, N, K, 3, 0.f, 0, stream, rs);
+    if (warps == 8) return launch_skinny<1, 8>(xp, wp, nullptr, M, N, K, 3, 0.f, 0, stream, rs);
+    return launch_skinny<1, 4>(xp, wp, nullptr, M, N, K, 3, 0.f, 0, stream, rs);
+  }
+  if (warps == 16) return launch_skinny<2, 16>(xp, wp, nullptr, M, N, K, 3, 0.f, 0, stream, rs);
+  if (warps == 8) return launch_skinny<2, 8>(xp, wp, nullptr, M, N, K, 3, 0.f, 0, stream, rs);
+  return launch_skinny<2, 4>(xp, wp, nullptr, M, N, K, 3, 0.f, 0, stream, rs);
 }

@@ -18,6 +18,7 @@ of the whole burst; chunks with nothing visible at a given step come out empty.
 from __future__ import annotations
 
 import dataclasses
+import gc
 from typing import Any, Sequence
 
 import numpy as np
@@ -154,8 +155,16 @@ class DecodeRunner:
       g.step_fn()
       self.stream.synchronize()
       before = self.ops.launches
-      with torch.cuda.graph(g.graph, stream=self.stream):
-        g.step_fn()
+      # No garbage collection while the stream captures: a collected object that frees device
+      # resources (an older graph, say) would make a call that a capture forbids and spoil it.
+      gc_was_on = gc.isenabled()
+      gc.disable()
+      try:
+        with torch.cuda.graph(g.graph, stream=self.stream):
+          g.step_fn()
+      finally:
+        if gc_was_on:
+          gc.enable()
       g.launches = self.ops.launches - before
     self.stream.synchronize()
     g.captured = True

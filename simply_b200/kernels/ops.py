@@ -100,6 +100,8 @@ class CudaOps:
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
     self.skinny_warps = 0
+    # False keeps the q, k, v projection and the rotation + cache write as two kernels (tests).
+    self.fused_qkv_rope = True
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
@@ -122,6 +124,8 @@ class CudaOps:
         "sb_soft_cap": [c_void, c_float, c_ll, c_void],
         "sb_gemm_f32_nt": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_void],
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
+        "sb_qkv_rope_skinny": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
+                               c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_int, c_void],
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
@@ -472,6 +476,33 @@ class CudaOps:
                _ptr(ctx.positions), t, num_heads, num_kv_heads, head_dim, ctx.page_size,
                storage.shape[0] if storage is not None else 0, int(storage is not None), _ptr(self.err))
     return q
+
+  def project_rotate_store(self, x: torch.Tensor, w_qkv: torch.Tensor, tables, q_scale: float, num_heads: int,
+                           num_kv_heads: int, head_dim: int, storage: torch.Tensor | None,
+                           block_table: torch.Tensor, ctx: Any) -> torch.Tensor:
+    """The fused q, k, v projection, then rotation, query scale and the stores: queries
+    [T, num_heads, head_dim] are returned, keys and values go into the pages of `storage`.
+
+    Steps of a few tokens do it in one kernel (the product's epilogue rotates and stores);
+    larger ones as a product followed by `rope_and_cache_write`.
+    """
+    t, k = x.shape
+    if (self.fused_qkv_rope and self.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+        and t <= self.skinny_max_rows and t <= 16 and head_dim % 32 == 0 and k % 8 == 0):
+      x = self.cast(x, torch.bfloat16)
+      q = self._new(t, num_heads, head_dim, dtype=torch.bfloat16)
+      cos, sin = tables if tables is not None else (None, None)
+      if storage is not None and storage.dtype != torch.bfloat16:
+        raise KernelError("cache and activations must share one dtype")
+      rc = self._call("sb_qkv_rope_skinny", _ptr(x), _ptr(w_qkv), t, k, _ptr(cos), _ptr(sin), float(q_scale),
+                      _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
+                      _ptr(ctx.positions), num_heads, num_kv_heads, head_dim, ctx.page_size,
+                      storage.shape[0] if storage is not None else 0, _ptr(self.err), self.skinny_warps)
+      if rc == 0:
+        return q
+    qkv = self.linear(x, w_qkv)
+    return self.rope_and_cache_write(qkv, tables, q_scale, num_heads, num_kv_heads, head_dim, storage,
+                                     block_table, ctx)
 
   # ---- attention ------------------------------------------------------------
   def paged_attention(self, q: torch.Tensor, storage: torch.Tensor, block_table: torch.Tensor, ctx: Any, *,

@@ -71,11 +71,10 @@ class PagedAttention(Mixer):
     ops = ctx.ops
     if writes_cache and not self.project_kv:
       raise ValueError(f"{self.prefix}: a mixer without k/v projections cannot write a cache")
-    qkv = ops.linear(x, self.qkv_weight)
     tables = self.position.rotation_tables(ctx, self.head_dim)
     block_table = ctx.block_tables[cache.group]
-    q = ops.rope_and_cache_write(
-        qkv, tables, self.query_scale, self.num_heads, self.num_kv_heads if self.project_kv else 0,
+    q = ops.project_rotate_store(
+        x, self.qkv_weight, tables, self.query_scale, self.num_heads, self.num_kv_heads if self.project_kv else 0,
         self.head_dim, cache.storage if writes_cache else None, block_table, ctx)
     o = ops.paged_attention(
         q, cache.storage, block_table, ctx, num_heads=self.num_heads,

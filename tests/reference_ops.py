@@ -101,6 +101,11 @@ class ReferenceOps:
     angle = positions.float()[:, None] / timescale[None, :] / np.float32(scale_factor)
     return torch.cos(angle), torch.sin(angle)
 
+  def project_rotate_store(self, x, w_qkv, tables, q_scale, num_heads, num_kv_heads, head_dim, storage,
+                           block_table, ctx):
+    return self.rope_and_cache_write(self.linear(x, w_qkv), tables, q_scale, num_heads, num_kv_heads, head_dim,
+                                     storage, block_table, ctx)
+
   def rope_and_cache_write(self, qkv, tables, q_scale, num_heads, num_kv_heads, head_dim, storage,
                            block_table, ctx):
     t = qkv.shape[0]

@@ -151,6 +151,44 @@ def test_rope_and_cache_write(table, dtype, hq, hkv, dh, ps):
         q_only, dtype)
 
 
+@pytest.mark.parametrize("hq,hkv,dh,ps,width", [(4, 1, 32, 4, 72), (6, 2, 96, 8, 200), (3, 3, 256, 64, 1000),
+                                                 (8, 4, 64, 16, 520)])
+@pytest.mark.parametrize("seqs", [[(0, 9), (37, 1), (130, 6)], [(5, 1)], [(63, 1), (64, 1), (200, 1), (7, 1), (0, 1)]],
+                         ids=["mixed16", "one", "decode5"])
+def test_project_rotate_store_fused(table, hq, hkv, dh, ps, width, seqs):
+  """The one-kernel projection + rotation + cache write of small steps against the two-kernel path
+  and the plain statement: queries, written cache rows, and nothing else touched."""
+  dtype = torch.bfloat16
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=None, page_size=ps, dtype=dtype,
+                     device="cuda", ops=ops, seed=5)
+  t = sc.ctx.num_tokens
+  assert t <= 16
+  x = torch.randn(t, width).to(dtype).cuda()
+  w = (torch.randn((hq + 2 * hkv) * dh, width) / width ** 0.5).to(dtype).cuda()
+  rot = ops.rotation_tables(sc.ctx.positions, torch.linspace(1, 900, dh // 2).cuda(), 1.0)
+  st_ref, st_two = sc.storage.clone(), sc.storage.clone()
+  q_ref = ref.project_rotate_store(x, w, rot, 0.37, hq, hkv, dh, st_ref,
+                                   sc.block_table, sc.ctx)
+  before = ops.launches
+  q = ops.project_rotate_store(x, w, rot, 0.37, hq, hkv, dh, sc.storage, sc.block_table, sc.ctx)
+  assert ops.launches - before == 1  # one kernel
+  ops.check_errors()
+  ops.fused_qkv_rope = False
+  try:
+    q_two = ops.project_rotate_store(x, w, rot, 0.37, hq, hkv, dh, st_two, sc.block_table, sc.ctx)
+  finally:
+    ops.fused_qkv_rope = True
+  close(q, q_ref, dtype, 3.0)
+  close(q, q_two, dtype, 3.0)
+  torch.testing.assert_close(sc.storage.float().cpu(), st_ref.float().cpu(), equal_nan=True, **tol(dtype, 3.0))
+  torch.testing.assert_close(sc.storage.float().cpu(), st_two.float().cpu(), equal_nan=True, **tol(dtype, 3.0))
+  # Without rotation and without a cache (a layer that reads another layer's cache).
+  wq = w[:hq * dh]
+  q_plain = ops.project_rotate_store(x, wq, None, 1.0, hq, 0, dh, None, sc.block_table, sc.ctx)
+  close(q_plain.reshape(t, -1), ref.linear(x, wq), dtype, 3.0)
+
+
 # ---- feed-forward pieces ---------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("act", [0, 1, 2])
