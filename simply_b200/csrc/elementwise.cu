@@ -69,19 +69,78 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
                                      float eps_pre, int pre_plus_one, const int* __restrict__ rows,
                                      T* __restrict__ y, int width, int num_rows_total, int* err) {
   pdl_launch_dependents();
-  pdl_wait();
   extern __shared__ float row[];  // width floats + 33 scratch
   float* scratch = row + width;
   const int r = blockIdx.x;
+  constexpr int N = Vec<T>::N;
+  const bool vec = width % N == 0;
+  const bool one_chunk = vec && width <= (int)blockDim.x * N;
+  // The norm scales are weights, which no kernel writes: they are fetched before the wait for
+  // the kernel's inputs.  (Launching this kernel early as well made the whole step slower: the
+  // products on both sides of it then overlap each other's weight streams.)
+  float wp[N], wq[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) wp[k] = wq[k] = 0.f;
+  if (one_chunk && (int)threadIdx.x * N < width) {
+    if (branch && w_post) load_scalars<N>(w_post, post_f32, threadIdx.x * N, wp);
+    if (w_pre) load_scalars<N>(w_pre, pre_f32, threadIdx.x * N, wq);
+  }
+  pdl_wait();
   int src = rows ? rows[r] : r;
   if (src < 0 || src >= num_rows_total) {
     if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_ROW);
     src = 0;
   }
   float* hp = h + (size_t)src * width;
-  constexpr int N = Vec<T>::N;
-  const bool vec = width % N == 0;
   const float post_one = post_plus_one ? 1.f : 0.f, pre_one = pre_plus_one ? 1.f : 0.f;
+  if (one_chunk) {
+    // The row fits one 16-byte chunk per thread: every load is issued before the first sum, so
+    // the kernel pays one memory latency instead of one per pass.  Same arithmetic as below.
+    const int i = threadIdx.x * N;
+    const bool on = i < width;
+    float b[N], v[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k) b[k] = v[k] = 0.f;
+    if (on) {
+      if (branch) Vec<T>::load(branch + (size_t)src * width + i, b);
+#pragma unroll
+      for (int k = 0; k < N; k += 4) Vec<float>::load(hp + i + k, v + k);
+    }
+    if (branch) {
+      float rstd_b = 1.f;
+      if (w_post) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < N; ++k) ss += b[k] * b[k];
+        ss = block_sum(ss, scratch);
+        rstd_b = 1.0f / sqrtf(ss / (float)width + eps_post);
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        float bb = b[k];
+        if (w_post) bb = bb * rstd_b * (wp[k] + post_one);
+        v[k] += bb;
+      }
+      if (!rows && on) {
+#pragma unroll
+        for (int k = 0; k < N; k += 4) Vec<float>::store(hp + i + k, v + k);
+      }
+    }
+    if (w_pre) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < N; ++k) ss += v[k] * v[k];
+      ss = block_sum(ss, scratch);
+      const float rstd = 1.0f / sqrtf(ss / (float)width + eps_pre);
+      if (on) {
+        float o[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) o[k] = v[k] * rstd * (wq[k] + pre_one);
+        Vec<T>::store(y + (size_t)r * width + i, o);
+      }
+    }
+    return;
+  }
   float rstd_b = 1.f;
   if (branch) {
     const T* bp = branch + (size_t)src * width;
