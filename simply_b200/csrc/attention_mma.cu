@@ -240,8 +240,8 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
 // ---------------------------------------------------------------------------------------
 template <int WM, int WN>
 __global__ void __launch_bounds__(WM * WN * 32) attn_prefill_kernel(const AttnParams p) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   constexpr int BM = WM * 16, THREADS = WM * WN * 32, KEYS = BN / WN;  // keys of a tile per warp
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [BM][PITCH]
@@ -371,8 +371,8 @@ constexpr int DEC_NT = DEC_WARPS * 32;
 constexpr int DEC_STAGES = 3;
 
 __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p, int* work_counter, int total_work) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sq = reinterpret_cast<bf16*>(smem_raw);  // [16][PITCH]
   bf16* sk = sq + 16 * PITCH;                    // [STAGES][DEC_BN][PITCH]
@@ -575,8 +575,8 @@ template <bool USE_TMA>
 __global__ void __launch_bounds__(D8_NT)
 attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work, const __grid_constant__ CUtensorMap tmap,
                     int box_rows) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   constexpr int TILE_ELEMS = USE_TMA ? D8_BN * DH : D8_BN * PITCH;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // The swizzle pattern is a function of the address: tiles start on a 1024-byte boundary
@@ -885,7 +885,6 @@ __device__ __forceinline__ void mbar_arrive_one(uint64_t* bar) {
 __global__ void __launch_bounds__(WS_NT)
 attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, const __grid_constant__ CUtensorMap tmap,
                       int box_rows) {
-  pdl_launch_dependents();
   constexpr int TILE_ELEMS = D8_BN * DH;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* aligned = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -987,6 +986,7 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
     const int rows_valid = w.q_len * group;  // <= 8 by the host's routing
     const size_t pidx = (size_t)(work / p.num_kv_heads) * p.num_kv_heads + w.m;
     pdl_wait();  // before the first read of a query and the first write of a result
+    pdl_launch_dependents();
     if (w.n_tiles == 0) {
       // Nothing of this chunk is visible: an empty partial result.
       if (warp == 0) {
@@ -1163,7 +1163,6 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
                     const int* __restrict__ split_start, const int* __restrict__ split_count,
                     bf16* __restrict__ out, int num_q_heads, int num_kv_heads, int rows_max,
                     int* __restrict__ work_counter) {
-  pdl_launch_dependents();
   __shared__ float s_acc[COMBINE_WARPS][DH];
   __shared__ float s_den[COMBINE_WARPS];
   __shared__ float s_max[COMBINE_WARPS];
@@ -1177,6 +1176,7 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   const size_t base = ((size_t)split_start[b] * num_kv_heads + m) * rows_max + r;
   const size_t stride = (size_t)num_kv_heads * rows_max;  // from one chunk's partial to the next
   pdl_wait();
+  pdl_launch_dependents();
   // The split-key kernel has finished: put its work counter back to zero for the next launch.
   if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0;
   if (count <= 0) return;  // this sequence went through the prefill kernel

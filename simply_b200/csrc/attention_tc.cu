@@ -84,8 +84,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __global__ void __launch_bounds__(TC_THREADS)
 attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sq = base;                               // [SLABS][128 rows][128 B]

@@ -112,24 +112,27 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 // Programmatic dependent launch.  Every kernel of the engine begins with
-// `pdl_launch_dependents(); pdl_wait();` (or does work that depends on nothing written by
-// earlier kernels, such as fetching weights, between the two).  The first lets the next
-// kernel of the stream start as soon as all blocks of this one have started; the second
-// blocks until every earlier kernel has finished and its writes are visible.  Launched
-// without the attribute both are no-ops, so a kernel is always correct on its own.
+// `pdl_wait(); pdl_launch_dependents();` (or does work that depends on nothing written by
+// earlier kernels, such as fetching weights, before the two).  The wait blocks until every
+// earlier kernel has finished and its writes are visible; the trigger lets the next kernel of
+// the stream start once all blocks of this one have passed it.  Trigger after wait: at most
+// two kernels then overlap (this one, and the next up to its own wait).  Triggering before the
+// wait lets a whole chain of kernels pile up on the device ahead of time, which was measured to
+// slow a decode step by a fifth.  Launched without the attribute both are no-ops, so a kernel
+// is always correct on its own.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 #include <stdlib.h>
 
-// SIMPLY_B200_PDL in the environment: 0 launches every kernel the plain way, 1 lets every
-// kernel start early, 2 (the default) only those that have something to do before their
-// inputs are ready (the weight-streaming products).
+// SIMPLY_B200_PDL in the environment: 0 launches every kernel the plain way, 1 (the default)
+// lets every kernel start early, 2 only those that have something to do before their inputs are
+// ready (the weight-streaming products, attention over older keys).
 inline int sb_pdl_level() {
   static int level = -1;
   if (level < 0) {
     const char* e = getenv("SIMPLY_B200_PDL");
-    level = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
+    level = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
   }
   return level;
 }

@@ -62,7 +62,6 @@ template <int MT, int WARPS, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void* __restrict__ out, int M,
                    int N, int K, float cap, int act, const RopeStore rs) {
-  pdl_launch_dependents();
   constexpr int SETS = EPI >= 2 ? 2 : 1;
   __shared__ float partial[WARPS][SETS][MT][16][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -117,6 +116,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
   };
   load_weights(wa, warp);
   pdl_wait();
+  pdl_launch_dependents();
   for (int s0 = warp; s0 < steps; s0 += STRIDE) {
     uint4 xv[UNROLL][MT];
 #pragma unroll

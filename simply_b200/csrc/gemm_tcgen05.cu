@@ -28,8 +28,8 @@ template <int BN, bool OUT_F32>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ out, int M, int N, int K, float cap, int* err) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
