@@ -16,9 +16,11 @@
 //   O[128 x DH] += P . V       tcgen05.mma, accumulator in tensor memory for the whole walk
 // Roles: warp 0 TMA producer of Q (once) and of the key tiles, warp 2 of the value tiles (both
 // from the paged cache through the block table), warp 1 MMA issue (one thread), warps 4..19
-// softmax and epilogue: four threads per query row with 16 of the tile's 64 columns each (one
-// thread per row leaves each scheduler a single warp, and the instruction latency of the
-// softmax then bounds the tile).  The running maximum is only moved when it grows by more than 8 (log2 units):
+// softmax and epilogue: two groups of 8 warps that take the key tiles in turn, two threads per
+// query row in a group with 32 of the tile's 64 columns each.  (One thread per row leaves each
+// scheduler a single warp, and one group of warps has to finish a tile's softmax before it can
+// start the next: both leave the tensor cores waiting for the softmax's instruction latency.)
+// The running maximum is only moved when it grows by more than 8 (log2 units):
 // O is then rescaled in tensor memory; otherwise numerators up to 2^8 are kept, which float32
 // and bfloat16 hold without loss, and the final division by the row sum makes it exact.
 // All waits are bounded; a wait that runs out sets SB_ERR_TIMEOUT and the block leaves after
@@ -42,11 +44,12 @@ constexpr int DH = SB_HEAD_DIM;
 constexpr int BM = 128, BN = 64, SLABS = DH / 64;
 constexpr int Q_BYTES = BM * DH * 2, KV_TILE_BYTES = BN * DH * 2, P_BYTES = BM * BN * 2;
 constexpr int KV_STAGES = 2;
-constexpr int SPLIT = 4;           // softmax threads per query row
+constexpr int GROUPS = 2;          // softmax groups: group g takes the key tiles j with j % 2 == g
+constexpr int SPLIT = 2;           // softmax threads per query row within a group
 constexpr int CW = BN / SPLIT;     // columns of a key tile per softmax thread
-constexpr int OW = DH / SPLIT;     // columns of O per softmax thread (rescale, epilogue)
-static_assert(CW == 16 && OW % 16 == 0, "tensor-memory loads of 16 columns");
-constexpr int TC_THREADS = 128 + 128 * SPLIT;  // warps: key producer, MMA, value producer, spare, 4 * SPLIT softmax
+constexpr int OW = DH / (GROUPS * SPLIT);  // columns of O per softmax thread in the epilogue
+static_assert(CW == 32 && OW % 16 == 0, "tensor-memory loads of 32 and 16 columns");
+constexpr int TC_THREADS = 128 + 128 * GROUPS * SPLIT;  // warps: key producer, MMA, value producer, spare, softmax
 constexpr int S_COL0 = 0, O_COL0 = 2 * BN;  // S buffers at columns 0 and 64, O from column 128
 constexpr int TMEM_COLS = O_COL0 + DH <= 256 ? 256 : 512;  // a power of two that holds S, S and O
 constexpr float LOG2E = 1.4426950408889634f;
@@ -93,8 +96,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   unsigned char* sv = sk + KV_STAGES * KV_TILE_BYTES;     // [STAGES][SLABS][64 keys][128 B]
   unsigned char* sp = sv + KV_STAGES * KV_TILE_BYTES;     // [128 rows][128 B]
   __shared__ __align__(8) uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES],
-      v_empty[KV_STAGES], s_full[2], s_empty[2], p_ready, pv_done, x_bar[4];
-  __shared__ float row_max[2][SPLIT][BM];  // the parts' row maxima of a tile (at the end: row sums)
+      v_empty[KV_STAGES], s_full[2], s_empty[2], p_ready, pv_done[2], x_bar[GROUPS][4], m_bar[2][4], l_bar[4];
+  __shared__ float row_max[GROUPS][SPLIT][BM];  // the parts' row maxima of a group's tile
+  __shared__ float row_m[2][BM];                // the running maximum after a tile, by tile parity
+  __shared__ float row_sum[GROUPS * SPLIT][BM]; // at the end: the threads' partial row sums
   __shared__ uint32_t tmem_slot;
   __shared__ int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,9 +128,15 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 4 * SPLIT);
     }
-    for (int q = 0; q < 4; ++q) mbar_init(&x_bar[q], SPLIT);
+    for (int q = 0; q < 4; ++q) {
+      for (int g = 0; g < GROUPS; ++g) mbar_init(&x_bar[g][q], SPLIT);
+      mbar_init(&m_bar[0][q], SPLIT);
+      mbar_init(&m_bar[1][q], SPLIT);
+      mbar_init(&l_bar[q], GROUPS * SPLIT);
+    }
     mbar_init(&p_ready, 4 * SPLIT);
-    mbar_init(&pv_done, 1);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
     s_failed = 0;
     mbar_fence_init();
   }
@@ -217,16 +228,25 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           tc_mma_f16(tmem + O_COL0, a, bdesc, idesc_pv, j > 0 || kk > 0);
         }
         tc_commit(&v_empty[s]);
-        tc_commit(&pv_done);
+        tc_commit(&pv_done[j & 1]);
       }
       if (!ok) s_failed = 1;
     }
   } else if (warp >= 4) {
-    // ---- softmax and epilogue: SPLIT threads per query row, CW of the tile's 64 columns each ---------
-    // A warp may only touch the 32 lanes of tensor memory that (warp % 4) names, so the SPLIT
-    // threads of a row sit in the warps quarter, quarter + 4, ...  They agree on the row's
-    // maximum through shared memory once per tile; row sums stay partial until the end.
-    const int quarter = warp & 3, part = (warp - 4) >> 2;
+    // ---- softmax and epilogue ---------------------------------------------------------------------
+    // Two groups of 8 warps; group g takes the key tiles j with j % 2 == g, so that the softmax of
+    // one tile runs while the other group's tile is still on its way (one group alone is bound by
+    // the latency of its own instruction chain).  Within a group SPLIT threads share a query row,
+    // CW of the tile's 64 columns each; a warp may only touch the 32 lanes of tensor memory that
+    // (warp % 4) names, so the threads of a row sit in the warps quarter, quarter + 4, ...
+    // Barriers that both groups use in turn exist once per tile parity (m_bar, pv_done): a thread
+    // then waits on every phase of the barriers it waits on, never on every other one, which a
+    // wait by phase parity could not tell apart.
+    // What passes from tile to tile is the row's running maximum: the group of tile j publishes it
+    // (row_m, m_bar) as soon as it has seen the tile's maxima, long before its P is written.  Row
+    // sums stay partial in every thread, each relative to the maximum that thread saw last.
+    const int quarter = warp & 3, sw = (warp - 4) >> 2;  // sw: 0 .. GROUPS * SPLIT - 1
+    const int grp = sw / SPLIT, part = sw % SPLIT;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int pos = r < rows_valid ? p0 + r / group : -1;
@@ -235,18 +255,19 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     const int warp_pos_lo = p0 + (quarter * 32) / group, warp_pos_hi = p0 + (quarter * 32 + 31) / group;
     const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
     const float scale2 = p.cap > 0.f ? p.cap * LOG2E : LOG2E;  // from x (tanh's value, or the score) to log2 units
-    float m_use = -INFINITY, l = 0.f;
+    float m_own = -INFINITY, l = 0.f;  // the maximum this thread's sum is relative to; the sum
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = grp; j < n_tiles; j += GROUPS) {
       const int sb = j & 1, s = j % KV_STAGES;
       const int j0 = tile0 + j * BN;
+      const int use = j / GROUPS;  // how often this group's barriers have been used
       if (!mbar_wait_bounded(&s_full[sb], (j / 2) & 1)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
       uint32_t sr[CW];
-      tmem_load_32x16(tmem + lane_base + S_COL0 + sb * BN + part * CW, sr);
+      tmem_load_32x32(tmem + lane_base + S_COL0 + sb * BN + part * CW, sr);
       tmem_wait_load();
       tc_fence_before_sync();
       __syncwarp();
@@ -272,22 +293,37 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           mx = fmaxf(mx, v);
         }
       }
-      // The row's maximum over all parts.
-      row_max[j & 1][part][r] = mx;
+      // The row's maximum over the group's parts.
+      row_max[grp][part][r] = mx;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&x_bar[quarter]);
-      if (!mbar_wait_bounded(&x_bar[quarter], j & 1)) {
+      if (lane == 0) mbar_arrive(&x_bar[grp][quarter]);
+      if (!mbar_wait_bounded(&x_bar[grp][quarter], use & 1)) {
         ok = false;
         break;
       }
 #pragma unroll
-      for (int q = 0; q < SPLIT; ++q) mx = fmaxf(mx, row_max[j & 1][q][r]);
+      for (int q = 0; q < SPLIT; ++q) mx = fmaxf(mx, row_max[grp][q][r]);
       mx *= scale2;
-      // Move the running maximum only when it grows by more than the threshold.
-      float alpha = 1.f;
-      if (mx > m_use + RESCALE_THRESHOLD || (m_use == -INFINITY && mx != -INFINITY)) {
-        alpha = fast_exp2(m_use - mx);  // 0 when there was no maximum yet
-        m_use = mx;
+      // The running maximum after the tile before this one (the other group's), then after this
+      // one: it only moves when it grows by more than the threshold.  Every part of the group
+      // decides alike and publishes; the other group waits for it at its next tile.
+      float m_prev = -INFINITY;
+      if (j > 0) {
+        if (!mbar_wait_bounded(&m_bar[(j - 1) & 1][quarter], ((j - 1) / 2) & 1)) {
+          ok = false;
+          break;
+        }
+        m_prev = row_m[(j - 1) & 1][r];
+      }
+      float m_use = m_prev;
+      if (mx > m_prev + RESCALE_THRESHOLD || (m_prev == -INFINITY && mx != -INFINITY)) m_use = mx;
+      if (part == 0) row_m[j & 1][r] = m_use;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&m_bar[j & 1][quarter]);
+      const float alpha = m_use == m_prev ? 1.f : fast_exp2(m_prev - m_use);  // for O; 0 when there was no maximum yet
+      if (m_use != m_own) {
+        l *= m_own == -INFINITY ? 0.f : fast_exp2(m_own - m_use);
+        m_own = m_use;
       }
       const float neg_base = m_use == -INFINITY ? 0.f : -m_use;
       float sum0 = 0.f, sum1 = 0.f;
@@ -299,16 +335,16 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         sum1 += e1;
         sr[c / 2] = pack_bf16(e0, e1);
       }
-      l = l * alpha + (sum0 + sum1);
+      l += sum0 + sum1;
       // P's buffer and O are free once the last tile's P.V is done.
-      if (j > 0 && !mbar_wait_bounded(&pv_done, (j - 1) & 1)) {
+      if (j > 0 && !mbar_wait_bounded(&pv_done[(j - 1) & 1], ((j - 1) / 2) & 1)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-        for (int c = part * OW; c < (part + 1) * OW; c += 16) {
+        for (int c = part * (DH / SPLIT); c < (part + 1) * (DH / SPLIT); c += 16) {
           uint32_t o[16];
           tmem_load_32x16(tmem + lane_base + O_COL0 + c, o);
           tmem_wait_load();
@@ -333,7 +369,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           ok = false;
           break;
         }
-        for (int i = threadIdx.x - 128; i < BN * SLABS * 8; i += 128 * SPLIT) {
+        for (int i = (quarter + 4 * part) * 32 + lane; i < BN * SLABS * 8; i += 128 * SPLIT) {
           const int key_row = (i / 8) % BN, sl = i / (8 * BN), c = i % 8;
           const int key = j0 + key_row;
           if (key < kv_lo || key >= kv_hi)
@@ -345,17 +381,19 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
-    // The row's sum over all parts.
-    if (ok) {
-      row_max[n_tiles & 1][part][r] = l;
+    // The row's sum over all threads that share it, each brought to the final maximum.
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait_bounded(&m_bar[(n_tiles - 1) & 1][quarter], ((n_tiles - 1) / 2) & 1);
+      const float m_final = ok ? row_m[(n_tiles - 1) & 1][r] : 0.f;
+      row_sum[sw][r] = (m_own == -INFINITY || m_final == -INFINITY) ? 0.f : l * fast_exp2(m_own - m_final);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&x_bar[quarter]);
-      ok = mbar_wait_bounded(&x_bar[quarter], n_tiles & 1);
+      if (lane == 0) mbar_arrive(&l_bar[quarter]);
+      ok = ok && mbar_wait_bounded(&l_bar[quarter], 0);
       l = 0.f;
 #pragma unroll
-      for (int q = 0; q < SPLIT; ++q) l += row_max[n_tiles & 1][q][r];
+      for (int q = 0; q < GROUPS * SPLIT; ++q) l += row_sum[q][r];
     }
-    if (ok && n_tiles > 0 && !mbar_wait_bounded(&pv_done, (n_tiles - 1) & 1)) ok = false;
+    if (ok && n_tiles > 0 && !mbar_wait_bounded(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) / 2) & 1)) ok = false;
     tc_fence_after_sync();
     if (ok) {
       // Every lane takes part in the warp-wide tensor-memory loads; only rows of the sequence store.
@@ -363,7 +401,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       const bool valid = r < rows_valid;
       bf16* op = p.out + ((size_t)(row0 + i0 + (valid ? r / group : 0)) * p.num_q_heads + m * group + (valid ? r % group : 0)) * DH;
 #pragma unroll 1
-      for (int c = part * OW; c < (part + 1) * OW; c += 16) {
+      for (int c = sw * OW; c < (sw + 1) * OW; c += 16) {
         uint32_t o[16];
         tmem_load_32x16(tmem + lane_base + O_COL0 + c, o);
         tmem_wait_load();
