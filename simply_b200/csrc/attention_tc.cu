@@ -11,8 +11,8 @@
 // A block owns 128 query rows of one (sequence, kv head): the G query heads of the group for
 // 128 / G consecutive tokens.  It walks the keys in tiles of 64:
 //   S[128 x 64]  = Q . K^T     tcgen05.mma, accumulator in tensor memory (two S buffers)
-//   P            = softmax numerators of S, written to shared memory as the next product's
-//                  128-row operand
+//   P            = softmax numerators of S as bfloat16, written over S in tensor memory: the
+//                  next product's 128-row operand comes from there
 //   O[128 x DH] += P . V       tcgen05.mma, accumulator in tensor memory for the whole walk
 // Roles: warp 0 TMA producer of Q (once) and of the key tiles, warp 2 of the value tiles (both
 // from the paged cache through the block table), warp 1 MMA issue (one thread), warps 4..19
@@ -42,7 +42,7 @@ using namespace sbx;
 
 constexpr int DH = SB_HEAD_DIM;
 constexpr int BM = 128, BN = 64, SLABS = DH / 64;
-constexpr int Q_BYTES = BM * DH * 2, KV_TILE_BYTES = BN * DH * 2, P_BYTES = BM * BN * 2;
+constexpr int Q_BYTES = BM * DH * 2, KV_TILE_BYTES = BN * DH * 2;
 constexpr int KV_STAGES = 2;
 constexpr int GROUPS = 2;          // softmax groups: group g takes the key tiles j with j % 2 == g
 constexpr int SPLIT = 2;           // softmax threads per query row within a group
@@ -94,7 +94,6 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   unsigned char* sq = base;                               // [SLABS][128 rows][128 B]
   unsigned char* sk = sq + Q_BYTES;                       // [STAGES][SLABS][64 keys][128 B]
   unsigned char* sv = sk + KV_STAGES * KV_TILE_BYTES;     // [STAGES][SLABS][64 keys][128 B]
-  unsigned char* sp = sv + KV_STAGES * KV_TILE_BYTES;     // [128 rows][128 B]
   __shared__ __align__(8) uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES],
       v_empty[KV_STAGES], s_full[2], s_empty[2], p_ready, pv_done[2], x_bar[GROUPS][4], m_bar[2][4], l_bar[4];
   __shared__ float row_max[GROUPS][SPLIT][BM];  // the parts' row maxima of a group's tile
@@ -222,10 +221,11 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t a = smem_desc_sw128(sp + kk * 32, 16, 1024);
-          // 16 keys further = 16 rows of 128 bytes; the next 64 dims are one slab (BN * 128 bytes) further
+          // P comes from tensor memory, where it overwrote the tile's S: 16 keys are 8 columns of
+          // two bfloat16 each.  16 keys further in V = 16 rows of 128 bytes; the next 64 dims are
+          // one slab (BN * 128 bytes) further.
           const uint64_t bdesc = smem_desc_sw128(sv + s * KV_TILE_BYTES + kk * 16 * 128, BN * 128, 1024);
-          tc_mma_f16(tmem + O_COL0, a, bdesc, idesc_pv, j > 0 || kk > 0);
+          tc_mma_f16_ts(tmem + O_COL0, tmem + S_COL0 + (j & 1) * BN + kk * 8, bdesc, idesc_pv, j > 0 || kk > 0);
         }
         tc_commit(&v_empty[s]);
         tc_commit(&pv_done[j & 1]);
@@ -354,13 +354,14 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         }
         tmem_wait_store();
       }
-      // P as the 128-row operand of the next product: row r, 64 keys = 128 bytes, 16-byte chunks
-      // XOR-ed with the row's low three bits (the layout a 128-byte-swizzled TMA box would have).
-      unsigned char* prow = sp + r * 128;
+      // P as the 128-row operand of the next product, in tensor memory over the tile's S (all
+      // parts have read their S by now: they exchanged maxima since): row = lane, two keys per column.
+      {
+        uint32_t pw[16];
 #pragma unroll
-      for (int c = 0; c < CW / 8; ++c) {
-        const int chunk = part * (CW / 8) + c;
-        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
+        for (int c = 0; c < 16; ++c) pw[c] = sr[c];
+        tmem_store_32x16(tmem + lane_base + S_COL0 + sb * BN + part * (CW / 2), pw);
+        tmem_wait_store();
       }
       // Value rows of keys that are not the request's must read as zeros (0 * garbage could be NaN):
       // only in tiles that reach beyond [kv_lo, kv_hi).
@@ -375,8 +376,8 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           if (key < kv_lo || key >= kv_hi)
             *reinterpret_cast<uint4*>(sv + s * KV_TILE_BYTES + sl * (BN * 128) + key_row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
         }
+        fence_proxy_async();  // the zeroed value rows are visible to the tensor core's reads
       }
-      fence_proxy_async();  // P (and zeroed value rows) are visible to the tensor core's reads
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
@@ -426,7 +427,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-constexpr size_t TC_SMEM = (size_t)Q_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + P_BYTES + 1024;
+constexpr size_t TC_SMEM = (size_t)Q_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + 1024;
 
 }  // namespace
 

@@ -42,14 +42,17 @@ __device__ __forceinline__ unsigned long long sb_global_ns() {
   return t;
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
-  // A try_wait may itself block for a while, so the bound is on time (half a second), not on tries.
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = sb_global_ns();
-  for (;;) {
-    for (int spin = 0; spin < 64; ++spin)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (sb_global_ns() - start > 500000000ull) return false;
-    __nanosleep(100);
+  // A try_wait may itself block for a while, so the bound is on time (half a second), not on
+  // tries.  The clock is only read every 4096 tries: reading it, or sleeping, between two tries
+  // would add its latency to every hand-over between the warps of a pipeline.
+  unsigned long long start = 0;
+  for (unsigned tries = 1;; ++tries) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((tries & 0xFFFu) == 0) {
+      const unsigned long long now = sb_global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 500000000ull) return false;
+    }
   }
 }
 
