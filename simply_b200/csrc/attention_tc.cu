@@ -10,12 +10,14 @@
 //
 // A block owns 128 query rows of one (sequence, kv head): the G query heads of the group for
 // 128 / G consecutive tokens.  It walks the keys in tiles of 64:
-//   S[128 x 64]  = Q . K^T     tcgen05.mma, accumulator in tensor memory (two S buffers)
+//   S[128 x 64]  = Q . K^T     tcgen05.mma, accumulator in tensor memory (three S buffers: this
+//                              product runs two key tiles ahead of the one below)
 //   P            = softmax numerators of S as bfloat16, written over S in tensor memory: the
 //                  next product's 128-row operand comes from there
 //   O[128 x DH] += P . V       tcgen05.mma, accumulator in tensor memory for the whole walk
 // Roles: warp 0 TMA producer of Q (once) and of the key tiles, warp 2 of the value tiles (both
-// from the paged cache through the block table), warp 1 MMA issue (one thread), warps 4..19
+// from the paged cache through the block table), warps 1 and 3 MMA issue (one thread each: Q.K^T
+// and P.V), warps 4..19
 // softmax and epilogue: two groups of 8 warps that take the key tiles in turn, two threads per
 // query row in a group with 32 of the tile's 64 columns each.  (One thread per row leaves each
 // scheduler a single warp, and one group of warps has to finish a tile's softmax before it can
@@ -50,8 +52,10 @@ constexpr int CW = BN / SPLIT;     // columns of a key tile per softmax thread
 constexpr int OW = DH / (GROUPS * SPLIT);  // columns of O per softmax thread in the epilogue
 static_assert(CW == 32 && OW % 16 == 0, "tensor-memory loads of 32 and 16 columns");
 constexpr int TC_THREADS = 128 + 128 * GROUPS * SPLIT;  // warps: key producer, MMA, value producer, spare, softmax
-constexpr int S_COL0 = 0, O_COL0 = 2 * BN;  // S buffers at columns 0 and 64, O from column 128
-constexpr int TMEM_COLS = O_COL0 + DH <= 256 ? 256 : 512;  // a power of two that holds S, S and O
+constexpr int S_BUFS = 3;                               // S buffers: Q.K^T runs two key tiles ahead of P.V
+constexpr int S_COL0 = 0, O_COL0 = S_BUFS * BN;         // S buffers from column 0, O behind them
+constexpr int TMEM_COLS = O_COL0 + DH <= 256 ? 256 : 512;  // a power of two that holds the S buffers and O
+static_assert(O_COL0 + DH <= 512, "tensor memory has 512 columns");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.f;
 
@@ -95,7 +99,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   unsigned char* sk = sq + Q_BYTES;                       // [STAGES][SLABS][64 keys][128 B]
   unsigned char* sv = sk + KV_STAGES * KV_TILE_BYTES;     // [STAGES][SLABS][64 keys][128 B]
   __shared__ __align__(8) uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES],
-      v_empty[KV_STAGES], s_full[2], s_empty[2], p_ready, pv_done[2], x_bar[GROUPS][4], m_bar[2][4], l_bar[4];
+      v_empty[KV_STAGES], s_full[2 * S_BUFS], p_ready[4], pv_done[S_BUFS], o_done, x_bar[GROUPS][4], m_bar[2][4], l_bar[4];
   __shared__ float row_max[GROUPS][SPLIT][BM];  // the parts' row maxima of a group's tile
   __shared__ float row_m[2][BM];                // the running maximum after a tile, by tile parity
   __shared__ float row_sum[GROUPS * SPLIT][BM]; // at the end: the threads' partial row sums
@@ -123,19 +127,16 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4 * SPLIT);
-    }
+    for (int s = 0; s < 2 * S_BUFS; ++s) mbar_init(&s_full[s], 1);
     for (int q = 0; q < 4; ++q) {
       for (int g = 0; g < GROUPS; ++g) mbar_init(&x_bar[g][q], SPLIT);
       mbar_init(&m_bar[0][q], SPLIT);
       mbar_init(&m_bar[1][q], SPLIT);
       mbar_init(&l_bar[q], GROUPS * SPLIT);
     }
-    mbar_init(&p_ready, 4 * SPLIT);
-    mbar_init(&pv_done[0], 1);
-    mbar_init(&pv_done[1], 1);
+    for (int q = 0; q < 4; ++q) mbar_init(&p_ready[q], 4 * SPLIT);
+    for (int q = 0; q < S_BUFS; ++q) mbar_init(&pv_done[q], 1);
+    mbar_init(&o_done, 1);
     s_failed = 0;
     mbar_fence_init();
   }
@@ -189,32 +190,49 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issue (one thread) -------------------------------------------------------------------
+    // ---- MMA issue of S = Q.K^T (one thread) ----------------------------------------------------------
+    // Two threads issue the products, this one and warp 3's below: one thread alone spends about
+    // 70 cycles per instruction on the sixteen 128 x 64 x 16 products of a tile (they wait for Q
+    // and K from shared memory) and cannot feed the tensor cores.
+    // S(j) goes to buffer j % 3, which held S and then P of tile j - 3: its P.V must be done
+    // (pv_done[j % 3]: one barrier per buffer, since P.V may complete up to the tile before the one
+    // this thread is at, and a barrier shared by tiles j - 3 and j - 1 could then pass two phases
+    // before this thread looks, which a wait by phase parity cannot tell from none).
+    // The tile's barrier is s_full[j % 6], which only the softmax group of tile j waits on (a
+    // barrier that both groups waited on in turn would show each of them only every other phase,
+    // which a wait by phase parity cannot tell apart).
     if (lane == 0) {
       const uint32_t idesc_qk = idesc_bf16_f32(BM, BN, false, false);
-      const uint32_t idesc_pv = idesc_bf16_f32(BM, DH, false, true);  // V: the N index (dims) is contiguous
       bool ok = mbar_wait_bounded(&q_full, 0);
-      auto issue_qk = [&](int j) {
-        const int s = j % KV_STAGES, sb = j & 1;
-        if (!mbar_wait_bounded(&k_full[s], (j / KV_STAGES) & 1)) return false;
-        if (j >= 2 && !mbar_wait_bounded(&s_empty[sb], (j / 2 - 1) & 1)) return false;
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int s = j % KV_STAGES;
+        if (!mbar_wait_bounded(&k_full[s], (j / KV_STAGES) & 1) ||
+            (j >= S_BUFS && !mbar_wait_bounded(&pv_done[j % S_BUFS], ((j - S_BUFS) / S_BUFS) & 1))) {
+          ok = false;
+          break;
+        }
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < DH / 16; ++ks) {
           const uint64_t a = smem_desc_sw128(sq + (ks / 4) * (BM * 128) + (ks % 4) * 32, 16, 1024);
           const uint64_t bdesc = smem_desc_sw128(sk + s * KV_TILE_BYTES + (ks / 4) * (BN * 128) + (ks % 4) * 32, 16, 1024);
-          tc_mma_f16(tmem + S_COL0 + sb * BN, a, bdesc, idesc_qk, ks > 0);
+          tc_mma_f16(tmem + S_COL0 + (j % S_BUFS) * BN, a, bdesc, idesc_qk, ks > 0);
         }
-        tc_commit(&s_full[sb]);
+        tc_commit(&s_full[j % (2 * S_BUFS)]);
         tc_commit(&k_empty[s]);  // the key tile may be refilled once these MMAs have read it
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
+      }
+      if (!ok) s_failed = 1;
+    }
+  } else if (warp == 3) {
+    // ---- MMA issue of O += P.V (one thread) ---------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_pv = idesc_bf16_f32(BM, DH, false, true);  // V: the N index (dims) is contiguous
+      bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-        if (!ok) break;
         const int s = j % KV_STAGES;
-        if (!mbar_wait_bounded(&p_ready, j & 1) || !mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
+        // p_ready[j % 4]: the softmax may be two tiles ahead of this thread (S exists as soon as the
+        // P.V three tiles back is done), so tiles j and j + 2 must not share a barrier.
+        if (!mbar_wait_bounded(&p_ready[j % 4], (j / 4) & 1) || !mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
           ok = false;
           break;
         }
@@ -225,11 +243,13 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           // two bfloat16 each.  16 keys further in V = 16 rows of 128 bytes; the next 64 dims are
           // one slab (BN * 128 bytes) further.
           const uint64_t bdesc = smem_desc_sw128(sv + s * KV_TILE_BYTES + kk * 16 * 128, BN * 128, 1024);
-          tc_mma_f16_ts(tmem + O_COL0, tmem + S_COL0 + (j & 1) * BN + kk * 8, bdesc, idesc_pv, j > 0 || kk > 0);
+          tc_mma_f16_ts(tmem + O_COL0, tmem + S_COL0 + (j % S_BUFS) * BN + kk * 8, bdesc, idesc_pv, j > 0 || kk > 0);
         }
         tc_commit(&v_empty[s]);
-        tc_commit(&pv_done[j & 1]);
+        tc_commit(&pv_done[j % S_BUFS]);
       }
+      tc_commit(&o_done);  // every product into O is complete (a barrier of its own: the softmax
+                           // warps skip phases of pv_done, and the last one must not be mistaken)
       if (!ok) s_failed = 1;
     }
   } else if (warp >= 4) {
@@ -239,9 +259,9 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     // the latency of its own instruction chain).  Within a group SPLIT threads share a query row,
     // CW of the tile's 64 columns each; a warp may only touch the 32 lanes of tensor memory that
     // (warp % 4) names, so the threads of a row sit in the warps quarter, quarter + 4, ...
-    // Barriers that both groups use in turn exist once per tile parity (m_bar, pv_done): a thread
-    // then waits on every phase of the barriers it waits on, never on every other one, which a
-    // wait by phase parity could not tell apart.
+    // A barrier that both groups wait on in turn exists once per tile parity (m_bar): a thread then
+    // waits on every phase of it, never on every other one, which a wait by phase parity could not
+    // tell apart.
     // What passes from tile to tile is the row's running maximum: the group of tile j publishes it
     // (row_m, m_bar) as soon as it has seen the tile's maxima, long before its P is written.  Row
     // sums stay partial in every thread, each relative to the maximum that thread saw last.
@@ -258,10 +278,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     float m_own = -INFINITY, l = 0.f;  // the maximum this thread's sum is relative to; the sum
     bool ok = true;
     for (int j = grp; j < n_tiles; j += GROUPS) {
-      const int sb = j & 1, s = j % KV_STAGES;
+      const int sb = j % S_BUFS, s = j % KV_STAGES;
       const int j0 = tile0 + j * BN;
       const int use = j / GROUPS;  // how often this group's barriers have been used
-      if (!mbar_wait_bounded(&s_full[sb], (j / 2) & 1)) {
+      if (!mbar_wait_bounded(&s_full[j % (2 * S_BUFS)], (j / (2 * S_BUFS)) & 1)) {
         ok = false;
         break;
       }
@@ -269,9 +289,6 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       uint32_t sr[CW];
       tmem_load_32x32(tmem + lane_base + S_COL0 + sb * BN + part * CW, sr);
       tmem_wait_load();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[sb]);
       const bool need_mask = !rows_full || j0 + BN - 1 > warp_pos_lo || (p.window > 0 && warp_pos_hi - j0 >= p.window);
       float mx = -INFINITY;
       if (need_mask) {
@@ -336,13 +353,15 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         sr[c / 2] = pack_bf16(e0, e1);
       }
       l += sum0 + sum1;
-      // P's buffer and O are free once the last tile's P.V is done.
-      if (j > 0 && !mbar_wait_bounded(&pv_done[(j - 1) & 1], ((j - 1) / 2) & 1)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
+      // O may only be rescaled between the last tile's P.V and this one's.  (The phases of this
+      // barrier that are skipped here are long complete: a tile's S only exists once the P.V
+      // three tiles back is done.)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (!mbar_wait_bounded(&pv_done[(j - 1) % S_BUFS], ((j - 1) / S_BUFS) & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
 #pragma unroll 1
         for (int c = part * (DH / SPLIT); c < (part + 1) * (DH / SPLIT); c += 16) {
           uint32_t o[16];
@@ -366,7 +385,11 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       // Value rows of keys that are not the request's must read as zeros (0 * garbage could be NaN):
       // only in tiles that reach beyond [kv_lo, kv_hi).
       if (j0 < kv_lo || j0 + BN > kv_hi) {
-        if (!mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
+        // The value tile's barrier is only looked at in such tiles; its phase before this one is
+        // known to be complete once the P.V two tiles back is (whose phase before is complete in
+        // turn, as this tile's S exists).
+        if ((j >= KV_STAGES && !mbar_wait_bounded(&pv_done[(j - 2) % S_BUFS], ((j - 2) / S_BUFS) & 1)) ||
+            !mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
           ok = false;
           break;
         }
@@ -380,7 +403,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[j % 4]);
     }
     // The row's sum over all threads that share it, each brought to the final maximum.
     if (ok && n_tiles > 0) {
@@ -394,7 +417,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
 #pragma unroll
       for (int q = 0; q < GROUPS * SPLIT; ++q) l += row_sum[q][r];
     }
-    if (ok && n_tiles > 0 && !mbar_wait_bounded(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) / 2) & 1)) ok = false;
+    if (ok && !mbar_wait_bounded(&o_done, 0)) ok = false;
     tc_fence_after_sync();
     if (ok) {
       // Every lane takes part in the warp-wide tensor-memory loads; only rows of the sequence store.
