@@ -360,6 +360,34 @@ def test_paged_attention_random(table, dtype, hq, hkv, dh, ps, window, cap):
     close(got, want, dtype, 2.0)
 
 
+@pytest.mark.parametrize("hq,hkv,dh,ps,window,cap", [
+    (8, 4, 256, 64, None, 0.0), (8, 4, 256, 64, 1000, 50.0), (4, 1, 64, 16, None, 30.0), (16, 8, 128, 64, 300, 0.0),
+    (8, 1, 192, 32, None, 50.0)])
+def test_tcgen05_prefill_long_walks(table, hq, hkv, dh, ps, window, cap):
+  """Long portions through the tcgen05 prefill kernel: dozens of key tiles per block, so that its
+  warps (loaders, two issuers, two softmax groups) hand over to each other many times, with
+  scores spread so widely that the running maximum moves and O is rescaled again and again.
+  Run a few times: a hand-over that can miss a phase shows as a timed-out wait or a wrong row."""
+  dtype = torch.bfloat16
+  ops = table[dtype]
+  seqs = [(700, 1900), (0, 130), (64, 1)]
+  sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=dtype,
+                     device="cuda", ops=ops, seed=11)
+  q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 3.0).to(dtype).cuda()
+  ops.tensor_core_attention = False
+  try:
+    want = run_attention(ops, q, sc, hq, hkv, dh, cap, window)  # the general kernel
+  finally:
+    ops.tensor_core_attention = True
+  ops.check_errors()
+  for _ in range(4):
+    sc.ctx.memo.clear()
+    got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+    ops.check_errors()
+    assert torch.isfinite(got).all()
+    close(got, want, dtype, 2.0)
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("ps", [16, 64])
 @pytest.mark.parametrize("window", [None, 96])
