@@ -44,8 +44,15 @@ using namespace sbx;
 
 constexpr int DH = SB_HEAD_DIM;
 constexpr int BM = 128, BN = 64, SLABS = DH / 64;
-constexpr int Q_BYTES = BM * DH * 2, KV_TILE_BYTES = BN * DH * 2;
-constexpr int KV_STAGES = 2;
+// With a head size of 256 the first 128 dims of Q live in tensor memory (as the 128-row operand of
+// the first eight products of a tile, which then read only K from shared memory: with Q from
+// shared memory a 128 x 64 x 16 product waits about 75 cycles for its operands, twice what it
+// computes), the rest in shared memory, which leaves room for a third stage of keys.
+constexpr int QT_DIMS = DH == 256 ? 128 : 0;          // dims of Q in tensor memory
+constexpr int QT_COLS = QT_DIMS / 2;                  // two bfloat16 per column
+constexpr int QS_SLABS = SLABS - QT_DIMS / 64;        // slabs of 64 dims of Q in shared memory
+constexpr int Q_BYTES = BM * QS_SLABS * 128, KV_TILE_BYTES = BN * DH * 2;
+constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int GROUPS = 2;          // softmax groups: group g takes the key tiles j with j % 2 == g
 constexpr int SPLIT = 2;           // softmax threads per query row within a group
 constexpr int CW = BN / SPLIT;     // columns of a key tile per softmax thread
@@ -54,12 +61,14 @@ static_assert(CW == 32 && OW % 16 == 0, "tensor-memory loads of 32 and 16 column
 constexpr int TC_THREADS = 128 + 128 * GROUPS * SPLIT;  // warps: key producer, MMA, value producer, spare, softmax
 constexpr int S_BUFS = 3;                               // S buffers: Q.K^T runs two key tiles ahead of P.V
 constexpr int S_COL0 = 0, O_COL0 = S_BUFS * BN;         // S buffers from column 0, O behind them
-constexpr int TMEM_COLS = O_COL0 + DH <= 256 ? 256 : 512;  // a power of two that holds the S buffers and O
-static_assert(O_COL0 + DH <= 512, "tensor memory has 512 columns");
+constexpr int QT_COL0 = O_COL0 + DH;                    // Q's first dims behind O
+constexpr int TMEM_COLS = QT_COL0 + QT_COLS <= 256 ? 256 : 512;  // a power of two that holds the S buffers, O and Q's part
+static_assert(QT_COL0 + QT_COLS <= 512, "tensor memory has 512 columns");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.f;
 
 struct TcParams {
+  const bf16* q;  // [T, Hq, DH]
   const int* block_table;
   int max_pages;
   const int* cu_q;
@@ -95,11 +104,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sq = base;                               // [SLABS][128 rows][128 B]
-  unsigned char* sk = sq + Q_BYTES;                       // [STAGES][SLABS][64 keys][128 B]
-  unsigned char* sv = sk + KV_STAGES * KV_TILE_BYTES;     // [STAGES][SLABS][64 keys][128 B]
-  __shared__ __align__(8) uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES],
-      v_empty[KV_STAGES], s_full[2 * S_BUFS], p_ready[4], pv_done[S_BUFS], o_done, x_bar[GROUPS][4], m_bar[2][4], l_bar[4];
+  unsigned char* sq = base;                               // [QS_SLABS][128 rows][128 B]
+  unsigned char* sk = sq + Q_BYTES;                       // [K_STAGES][SLABS][64 keys][128 B]
+  unsigned char* sv = sk + K_STAGES * KV_TILE_BYTES;      // [V_STAGES][SLABS][64 keys][128 B]
+  __shared__ __align__(8) uint64_t q_full, qt_ready, k_full[K_STAGES], v_full[V_STAGES], s_full[2 * S_BUFS], p_ready[4], pv_done[S_BUFS], o_done, x_bar[GROUPS][4], m_bar[2][4], l_bar[4];
   __shared__ float row_max[GROUPS][SPLIT][BM];  // the parts' row maxima of a group's tile
   __shared__ float row_m[2][BM];                // the running maximum after a tile, by tile parity
   __shared__ float row_sum[GROUPS * SPLIT][BM]; // at the end: the threads' partial row sums
@@ -121,12 +129,9 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
-    }
+    mbar_init(&qt_ready, 4 * GROUPS * SPLIT);
+    for (int s = 0; s < K_STAGES; ++s) mbar_init(&k_full[s], 1);
+    for (int s = 0; s < V_STAGES; ++s) mbar_init(&v_full[s], 1);
     for (int s = 0; s < 2 * S_BUFS; ++s) mbar_init(&s_full[s], 1);
     for (int q = 0; q < 4; ++q) {
       for (int g = 0; g < GROUPS; ++g) mbar_init(&x_bar[g][q], SPLIT);
@@ -150,21 +155,28 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     // ---- producers (one thread each): warp 0 brings Q and the key tiles, warp 2 the value tiles.
     // Keys and values have rings of their own: a key tile is free as soon as its Q.K^T is done,
     // long before the value tile of the same keys, so the next keys arrive early.
+    // A stage of keys is free once the Q.K^T that read it is done (s_full of that tile), a stage of
+    // values once its P.V is (pv_done): the producers wait on those barriers, each on every phase.
     if (lane == 0) {
       const bool values = warp == 2;
       uint64_t* full = values ? v_full : k_full;
-      uint64_t* empty = values ? v_empty : k_empty;
       unsigned char* ring = values ? sv : sk;
-      if (!values) {
+      const int stages = values ? V_STAGES : K_STAGES;
+      if (!values && QS_SLABS > 0) {
         mbar_arrive_expect_tx(&q_full, Q_BYTES);
-        for (int sl = 0; sl < SLABS; ++sl)  // box: 64 dims x G heads x 128 / G tokens, rows in (token, head) order
-          tma_load_3d(sq + sl * (BM * 128), &map_q, sl * 64, m * group, row0 + i0, &q_full);
+        for (int sl = 0; sl < QS_SLABS; ++sl)  // box: 64 dims x G heads x 128 / G tokens, rows in (token, head) order
+          tma_load_3d(sq + sl * (BM * 128), &map_q, (sl + QT_DIMS / 64) * 64, m * group, row0 + i0, &q_full);
       }
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % KV_STAGES;
-        if (j >= KV_STAGES && !mbar_wait_bounded(&empty[s], (j / KV_STAGES - 1) & 1)) {
-          s_failed = 1;
-          break;
+        const int s = j % stages;
+        if (j >= stages) {
+          const int t = j - stages;  // the tile that used the stage before
+          const bool freed = values ? mbar_wait_bounded(&pv_done[t % S_BUFS], (t / S_BUFS) & 1)
+                                    : mbar_wait_bounded(&s_full[t % (2 * S_BUFS)], (t / (2 * S_BUFS)) & 1);
+          if (!freed) {
+            s_failed = 1;
+            break;
+          }
         }
         const int j0 = tile0 + j * BN;
         int boxes = 0;
@@ -203,10 +215,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     // which a wait by phase parity cannot tell apart).
     if (lane == 0) {
       const uint32_t idesc_qk = idesc_bf16_f32(BM, BN, false, false);
-      bool ok = mbar_wait_bounded(&q_full, 0);
+      bool ok = (QS_SLABS == 0 || mbar_wait_bounded(&q_full, 0)) && (QT_DIMS == 0 || mbar_wait_bounded(&qt_ready, 0));
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j % KV_STAGES;
-        if (!mbar_wait_bounded(&k_full[s], (j / KV_STAGES) & 1) ||
+        const int s = j % K_STAGES;
+        if (!mbar_wait_bounded(&k_full[s], (j / K_STAGES) & 1) ||
             (j >= S_BUFS && !mbar_wait_bounded(&pv_done[j % S_BUFS], ((j - S_BUFS) / S_BUFS) & 1))) {
           ok = false;
           break;
@@ -214,12 +226,17 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < DH / 16; ++ks) {
-          const uint64_t a = smem_desc_sw128(sq + (ks / 4) * (BM * 128) + (ks % 4) * 32, 16, 1024);
           const uint64_t bdesc = smem_desc_sw128(sk + s * KV_TILE_BYTES + (ks / 4) * (BN * 128) + (ks % 4) * 32, 16, 1024);
-          tc_mma_f16(tmem + S_COL0 + (j % S_BUFS) * BN, a, bdesc, idesc_qk, ks > 0);
+          if (ks < QT_DIMS / 16) {
+            // 16 dims of Q are 8 columns of two bfloat16 each
+            tc_mma_f16_ts(tmem + S_COL0 + (j % S_BUFS) * BN, tmem + QT_COL0 + ks * 8, bdesc, idesc_qk, ks > 0);
+          } else {
+            const int kq = ks - QT_DIMS / 16;
+            const uint64_t a = smem_desc_sw128(sq + (kq / 4) * (BM * 128) + (kq % 4) * 32, 16, 1024);
+            tc_mma_f16(tmem + S_COL0 + (j % S_BUFS) * BN, a, bdesc, idesc_qk, ks > 0);
+          }
         }
-        tc_commit(&s_full[j % (2 * S_BUFS)]);
-        tc_commit(&k_empty[s]);  // the key tile may be refilled once these MMAs have read it
+        tc_commit(&s_full[j % (2 * S_BUFS)]);  // also frees the key tile's stage
       }
       if (!ok) s_failed = 1;
     }
@@ -229,10 +246,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
       const uint32_t idesc_pv = idesc_bf16_f32(BM, DH, false, true);  // V: the N index (dims) is contiguous
       bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j % KV_STAGES;
+        const int s = j % V_STAGES;
         // p_ready[j % 4]: the softmax may be two tiles ahead of this thread (S exists as soon as the
         // P.V three tiles back is done), so tiles j and j + 2 must not share a barrier.
-        if (!mbar_wait_bounded(&p_ready[j % 4], (j / 4) & 1) || !mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
+        if (!mbar_wait_bounded(&p_ready[j % 4], (j / 4) & 1) || !mbar_wait_bounded(&v_full[s], (j / V_STAGES) & 1)) {
           ok = false;
           break;
         }
@@ -245,8 +262,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           const uint64_t bdesc = smem_desc_sw128(sv + s * KV_TILE_BYTES + kk * 16 * 128, BN * 128, 1024);
           tc_mma_f16_ts(tmem + O_COL0, tmem + S_COL0 + (j % S_BUFS) * BN + kk * 8, bdesc, idesc_pv, j > 0 || kk > 0);
         }
-        tc_commit(&v_empty[s]);
-        tc_commit(&pv_done[j % S_BUFS]);
+        tc_commit(&pv_done[j % S_BUFS]);  // also frees the value tile's stage
       }
       tc_commit(&o_done);  // every product into O is complete (a barrier of its own: the softmax
                            // warps skip phases of pv_done, and the last one must not be mistaken)
@@ -277,8 +293,25 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     const float scale2 = p.cap > 0.f ? p.cap * LOG2E : LOG2E;  // from x (tanh's value, or the score) to log2 units
     float m_own = -INFINITY, l = 0.f;  // the maximum this thread's sum is relative to; the sum
     bool ok = true;
+    if (QT_DIMS > 0) {
+      // Q's first dims to tensor memory: row = lane, this thread's 32 of them as 16 columns.
+      const bool valid = r < rows_valid;
+      const bf16* qrow = p.q + ((size_t)(row0 + i0 + (valid ? r / group : 0)) * p.num_q_heads + m * group + (valid ? r % group : 0)) * DH +
+                         sw * (QT_DIMS / (GROUPS * SPLIT));
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 v = valid ? *reinterpret_cast<const uint4*>(qrow + i * 8) : make_uint4(0, 0, 0, 0);
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+      }
+      tmem_store_32x16(tmem + lane_base + QT_COL0 + sw * (QT_COLS / (GROUPS * SPLIT)), w);
+      tmem_wait_store();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qt_ready);
+    }
     for (int j = grp; j < n_tiles; j += GROUPS) {
-      const int sb = j % S_BUFS, s = j % KV_STAGES;
+      const int sb = j % S_BUFS, s = j % V_STAGES;
       const int j0 = tile0 + j * BN;
       const int use = j / GROUPS;  // how often this group's barriers have been used
       if (!mbar_wait_bounded(&s_full[j % (2 * S_BUFS)], (j / (2 * S_BUFS)) & 1)) {
@@ -388,8 +421,8 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         // The value tile's barrier is only looked at in such tiles; its phase before this one is
         // known to be complete once the P.V two tiles back is (whose phase before is complete in
         // turn, as this tile's S exists).
-        if ((j >= KV_STAGES && !mbar_wait_bounded(&pv_done[(j - 2) % S_BUFS], ((j - 2) / S_BUFS) & 1)) ||
-            !mbar_wait_bounded(&v_full[s], (j / KV_STAGES) & 1)) {
+        if ((j >= V_STAGES && !mbar_wait_bounded(&pv_done[(j - 2) % S_BUFS], ((j - 2) / S_BUFS) & 1)) ||
+            !mbar_wait_bounded(&v_full[s], (j / V_STAGES) & 1)) {
           ok = false;
           break;
         }
@@ -450,7 +483,9 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-constexpr size_t TC_SMEM = (size_t)Q_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + 1024;
+constexpr size_t TC_SMEM = (size_t)Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + 1024;
+static_assert(QT_DIMS == 0 || QT_DIMS / (GROUPS * SPLIT) == 32, "each softmax thread stores 32 dims of Q");
+static_assert(V_STAGES == 2, "the zeroing of value rows looks two tiles back");
 
 }  // namespace
 
@@ -485,6 +520,7 @@ extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const
   const int box_rows = page_size < BN ? page_size : BN;
   if (sb_make_map_2d(&map_kv, cache, (long long)num_pages * 2 * num_kv_heads * page_size, DH, box_rows) != 0) return -12;
   TcParams p{};
+  p.q = (const bf16*)q;
   p.block_table = block_table; p.max_pages = max_pages; p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
   p.cap = cap; p.window = window; p.items = items; p.box_rows = box_rows; p.err = err;
