@@ -223,108 +223,21 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
   }
 }
 
-// The same, one warp per row with the row in registers: no shared memory, no block barrier.
-// For widths up to 16 vectors per lane (4096 bfloat16 or 2048 float32 values).
-#define RN_MAXC 16
-template <typename T>
-__global__ void __launch_bounds__(128)
-residual_norm_warp_kernel(float* __restrict__ h, const T* __restrict__ branch, const void* __restrict__ w_post,
-                          int post_f32, float eps_post, int post_plus_one, const void* __restrict__ w_pre,
-                          int pre_f32, float eps_pre, int pre_plus_one, const int* __restrict__ rows,
-                          T* __restrict__ y, int width, int num_rows, int num_rows_total, int* err) {
-  pdl_wait();
-  pdl_launch_dependents();
-  constexpr int N = Vec<T>::N;
-  const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= num_rows) return;
-  int src = rows ? rows[r] : r;
-  if (src < 0 || src >= num_rows_total) {
-    if (lane == 0) atomicOr(err, SB_ERR_BAD_ROW);
-    src = 0;
-  }
-  float* hp = h + (size_t)src * width;
-  const float post_one = post_plus_one ? 1.f : 0.f, pre_one = pre_plus_one ? 1.f : 0.f;
-  float v[RN_MAXC][N];
-  float ss = 0.f;
-  if (branch) {
-    const T* bp = branch + (size_t)src * width;
-#pragma unroll
-    for (int c = 0; c < RN_MAXC; ++c) {
-      const int i = (c * 32 + lane) * N;
-      if (i < width) {
-        Vec<T>::load(bp + i, v[c]);
-#pragma unroll
-        for (int k = 0; k < N; ++k) ss += v[c][k] * v[c][k];
-      }
-    }
-  }
-  float rstd_b = 1.f;
-  if (branch && w_post) rstd_b = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps_post);
-  ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < RN_MAXC; ++c) {
-    const int i = (c * 32 + lane) * N;
-    if (i < width) {
-      float hv[N], w[N];
-#pragma unroll
-      for (int k = 0; k < N; k += 4) Vec<float>::load(hp + i + k, hv + k);
-      if (branch) {
-        if (w_post) load_scalars<N>(w_post, post_f32, i, w);
-#pragma unroll
-        for (int k = 0; k < N; ++k) hv[k] += w_post ? v[c][k] * rstd_b * (w[k] + post_one) : v[c][k];
-        if (!rows) {
-#pragma unroll
-          for (int k = 0; k < N; k += 4) Vec<float>::store(hp + i + k, hv + k);
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < N; ++k) {
-        v[c][k] = hv[k];
-        ss += hv[k] * hv[k];
-      }
-    }
-  }
-  if (!w_pre) return;
-  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps_pre);
-  T* yp = y + (size_t)r * width;
-#pragma unroll
-  for (int c = 0; c < RN_MAXC; ++c) {
-    const int i = (c * 32 + lane) * N;
-    if (i < width) {
-      float w[N], o[N];
-      load_scalars<N>(w_pre, pre_f32, i, w);
-#pragma unroll
-      for (int k = 0; k < N; ++k) o[k] = v[c][k] * rstd * (w[k] + pre_one);
-      Vec<T>::store(yp + i, o);
-    }
-  }
-}
-
 extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const void* w_post, int post_f32,
                                 float eps_post, int post_plus_one, const void* w_pre, int pre_f32,
                                 float eps_pre, int pre_plus_one, const int* rows, void* y, int num_rows,
                                 int width, int num_rows_total, int* err, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  // Many rows of moderate width: one warp per row, the row in registers.  (With few rows a
-  // block per row finishes sooner, as 8 to 16 warps share the row.)
   const int vec = dtype == SB_DTYPE_F32 ? 4 : 8;
-  if (num_rows >= 64 && width % vec == 0 && width <= RN_MAXC * 32 * vec) {
-    const unsigned blocks = (unsigned)((num_rows + 3) / 4);
-    if (dtype == SB_DTYPE_F32)
-      sb_launch(residual_norm_warp_kernel<float>, blocks, 128, 0, stream, h, (const float*)branch, w_post, post_f32,
-                eps_post, post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (float*)y, width, num_rows,
-                num_rows_total, err);
-    else
-      sb_launch(residual_norm_warp_kernel<bf16>, blocks, 128, 0, stream, h, (const bf16*)branch, w_post, post_f32,
-                eps_post, post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (bf16*)y, width, num_rows,
-                num_rows_total, err);
-    SB_LAUNCH_CHECK();
-    return 0;
-  }
   const size_t smem = (size_t)(width + 33) * sizeof(float);
   if (smem > 200 * 1024) return -2;  // refused: row does not fit shared memory
-  const int threads = width >= 2048 ? 512 : 256;
+  // One 16-byte vector per thread where the row allows it: the kernel then issues all its loads
+  // at once, and its small blocks fill the SMs whether the step has eight rows or thousands.
+  // (One warp per row with the row in registers was tried for steps with many rows and is
+  // slower: 170 registers per thread leave an SM too few warps.)
+  int threads = width >= 2048 ? 512 : 256;
+  if (width % vec == 0 && width / vec <= 1024) threads = ((width / vec + 31) / 32) * 32;
+  if (threads < 64) threads = 64;
   if (dtype == SB_DTYPE_F32) {
     auto k = residual_norm_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
