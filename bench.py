@@ -319,6 +319,8 @@ def main(argv=None):
   for _ in range(args.warmup - 1):
     engine.step()
   torch.cuda.synchronize()
+  runner = engine._decode_runner
+  h2d0, d2h0 = runner.h2d_bytes, runner.d2h_bytes
   t0 = time.perf_counter()
   e2e_steps = 0
   while engine.has_unfinished() and e2e_steps < args.steps:
@@ -326,13 +328,11 @@ def main(argv=None):
     e2e_steps += 1
   torch.cuda.synchronize()
   e2e_s = time.perf_counter() - t0
+  h2d = (runner.h2d_bytes - h2d0) // max(e2e_steps, 1)  # counted where the copies are made
+  d2h = (runner.d2h_bytes - d2h0) // max(e2e_steps, 1)
   while engine.has_unfinished():
     engine.step()
   e2e_value = args.batch * e2e_steps / e2e_s
-  runner = engine._decode_runner
-  g = next(iter(runner.graphs.values()))
-  h2d = int(g.meta.numel() * 4)
-  d2h = int(args.batch * 4)
 
   clocks = sampler.stop()
   step_bytes = decode_bytes(cfg, layers, args.batch, context)

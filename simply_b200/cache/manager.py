@@ -57,6 +57,7 @@ class PageGroup:
     self.first_page = np.zeros(max_slots, dtype=np.int64)
     self.end_page = np.zeros(max_slots, dtype=np.int64)
     self.cache_names: list[str] = []
+    self.version = 0  # counts changes of `tables`: who holds a copy can tell whether it is current
 
   def plan(self, slot: int, cur_len: int, n_new: int) -> tuple[int, int]:
     """(pages to give back, pages to take) for `n_new` tokens after `cur_len` cached ones."""
@@ -73,6 +74,7 @@ class PageGroup:
     n_back, n_take = self.plan(slot, cur_len, n_new)
     if n_back == 0 and n_take == 0:
       return [], []  # the usual decode step: the token lands in a page the slot already holds
+    self.version += 1
     first, end = int(self.first_page[slot]), int(self.end_page[slot])
     row = self.tables[slot]
     back = [int(p) for p in row[first:first + n_back]]
@@ -88,6 +90,7 @@ class PageGroup:
     first, end = int(self.first_page[slot]), int(self.end_page[slot])
     back = [int(p) for p in self.tables[slot, first:end]]
     self.pool.give_back(back)
+    self.version += 1
     self.tables[slot, :] = -1
     self.first_page[slot] = 0
     self.end_page[slot] = 0
@@ -202,8 +205,27 @@ class CacheManager:
     return int(self.lengths[slot])
 
   # ---- pages ----------------------------------------------------------------
+  def changes_no_table(self, entries: Sequence[tuple[int, int]]) -> bool:
+    """True if the batch `[(slot, new tokens)]` neither takes nor gives back a page in any group
+    (the usual decode step).  One vectorised look instead of a plan per slot and group."""
+    if not entries:
+      return True
+    slots = np.fromiter((s for s, _ in entries), dtype=np.int64, count=len(entries))
+    new = np.fromiter((n for _, n in entries), dtype=np.int64, count=len(entries))
+    cur = self.lengths[slots]
+    for g in self.groups:
+      if np.any(-(-(cur + new) // self.page_size) > g.end_page[slots]):
+        return False
+      if g.window is not None:
+        first = np.minimum(np.maximum(cur - (g.window - 1), 0) // self.page_size, g.end_page[slots])
+        if np.any(first > g.first_page[slots]):
+          return False
+    return True
+
   def pages_short(self, entries: Sequence[tuple[int, int]]) -> int:
     """How many pages the batch `[(slot, new tokens)]` lacks (0 if it fits), worst group."""
+    if self.changes_no_table(entries):
+      return 0
     short = 0
     for g in self.groups:
       back = take = 0
@@ -221,6 +243,10 @@ class CacheManager:
       b, t = g.plan(slot, int(self.lengths[slot]), n_new)
       worst = max(worst, t - b)
     return worst
+
+  def tables_version(self) -> int:
+    """Changes whenever a block table of any group changes."""
+    return sum(g.version for g in self.groups)
 
   def min_free_pages(self) -> int:
     return min((g.pool.num_free for g in self.groups), default=1 << 30)
@@ -240,6 +266,10 @@ class CacheManager:
         raise ValueError(
             f"slot {slot}: {int(self.lengths[slot])} + {n} tokens exceed max_seq_len "
             f"{self.max_seq_len}")
+    if self.changes_no_table(entries):
+      for slot, n in entries:
+        self.lengths[slot] += n
+      return
     short = self.pages_short(entries)
     if short:
       raise OutOfPages(f"the step lacks {short} page(s)")

@@ -234,6 +234,14 @@ class CudaOps:
   DECODE_ITEM_COST = 48
 
   @staticmethod
+  def decode_chunk_range(q_start: np.ndarray, steps: int, window: int | None, chunk: int) -> tuple[np.ndarray, np.ndarray]:
+    """First and last chunk index per sequence that a decode burst of `steps` steps touches: from
+    the lowest key visible at the first step to the highest at the last."""
+    qs = np.asarray(q_start, dtype=np.int64)
+    lo = np.maximum(qs - window + 1, 0) // 64 * 64 if window else np.zeros_like(qs)
+    return lo // chunk, (qs + steps - 1) // chunk
+
+  @staticmethod
   def static_decode_plan(q_start: np.ndarray, steps: int, window: int | None, chunk: int,
                          items_per_seq: int) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
     """Work list of the split-key kernel for a decode burst replayed from a CUDA graph.
@@ -247,9 +255,8 @@ class CudaOps:
     b = len(q_start)
     items = np.full((b, items_per_seq, 2), -1, dtype=np.int32)
     count = np.zeros(b, dtype=np.int32)
-    for i, qs in enumerate(q_start.astype(np.int64)):
-      lo = max(int(qs) - window + 1, 0) // 64 * 64 if window else 0
-      first, last = lo // chunk, (int(qs) + steps - 1) // chunk
+    firsts, lasts = CudaOps.decode_chunk_range(q_start, steps, window, chunk)
+    for i, (first, last) in enumerate(zip(firsts.tolist(), lasts.tolist())):
       n = last - first + 1
       if n > items_per_seq:
         raise KernelError(f"decode burst needs {n} chunks per sequence, the graph holds {items_per_seq}")
