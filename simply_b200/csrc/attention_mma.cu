@@ -57,6 +57,7 @@ struct AttnParams {
   float* part_o;     // decode: [items, Hkv, rows_max, DH]
   float* part_ml;    // decode: [items, Hkv, rows_max, 2]
   int rows_max;
+  int older_keys_settled;  // decode: keys below q_start were written before the kernel just before this one
   int* err;
 };
 
@@ -920,6 +921,10 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
     if (lane != 0) return;
     unsigned seq = 0;  // tiles issued so far
     bool waited = false;
+    if (!p.older_keys_settled) {  // the caller cannot vouch for the older keys: wait before any tile
+      pdl_wait();
+      waited = true;
+    }
     for (unsigned wi = 0;; ++wi) {
       // The first item is the block's own index; further ones come from the counter.
       const int work = wi == 0 ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(work_counter, 1);
@@ -1326,13 +1331,17 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
 // part_o / part_ml: scratch of num_items * Hkv * rows_max * (DH | 2) floats;
 // work_counter: one int that is zero before the first launch; the merge kernel zeroes it again;
 // split_start / split_count: per sequence, its range of items (count 0: not handled here).
+// older_keys_settled: the caller vouches that every key and value below q_start was written
+// before the kernel launched just before this one (true inside the engine, where they come from
+// earlier steps); the kernel may then fetch them before that kernel has finished.
 extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int* block_table, int max_pages,
                                      const int* cu_q, const int* q_start, const int* token_seq, void* out,
                                      int num_tokens, int num_q_heads, int num_kv_heads, int page_size,
                                      int num_pages, float cap, int window, const int* items, int num_items,
                                      int chunk, float* part_o, float* part_ml, int* work_counter,
                                      int rows_max, const int* split_start, const int* split_count, int variant,
-                                     const void* tensor_map, int* err, cudaStream_t stream) {
+                                     const void* tensor_map, int older_keys_settled, int* err,
+                                     cudaStream_t stream) {
   // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel, fed by TMA through a
   // producer warp when a tensor map is given and the shapes allow); 1 forbids TMA; 2 uses TMA
   // without the producer warp; 16 forces the 16-row kernel.
@@ -1343,7 +1352,7 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.chunk = chunk; p.part_o = part_o; p.part_ml = part_ml;
-  p.rows_max = rows_max; p.err = err;
+  p.rows_max = rows_max; p.older_keys_settled = older_keys_settled; p.err = err;
   const int total_work = num_items * num_kv_heads;
   const bool power_of_two_pages = (page_size & (page_size - 1)) == 0;
   constexpr size_t ws_merge = (size_t)(D8_WARPS * 8 * DH) * sizeof(float);

@@ -57,6 +57,9 @@ class StepContext:
   host: dict[str, np.ndarray] = dataclasses.field(default_factory=dict)
   # Scratch shared by the parts of one step, e.g. rotation tables keyed by their parameters.
   memo: dict[Any, Any] = dataclasses.field(default_factory=dict)
+  # True when every cached key and value below q_start was written by an earlier step (the engine
+  # sets it): decode attention may then fetch them while the kernel before it still runs.
+  older_keys_settled: bool = False
 
 
 def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int],

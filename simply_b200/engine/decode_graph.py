@@ -124,7 +124,7 @@ class DecodeRunner:
         ops=ops, num_tokens=batch, num_seqs=batch, token_ids=view("token_ids"), positions=view("positions"),
         token_seq=view("token_seq"), cu_q=view("cu_q"), q_start=view("q_start"), slots=view("slots"),
         block_tables=block_tables, logit_rows=view("logit_rows"), max_q_len=1, max_kv_len=bucket,
-        page_size=eng.cache.page_size)
+        page_size=eng.cache.page_size, older_keys_settled=True)
     plans = {}
     for (window, group), per_seq in items_per_seq.items():
       plans[(window, group)] = dict(

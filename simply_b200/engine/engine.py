@@ -140,8 +140,10 @@ class Engine:
           raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
     lengths = [self.cache.length(e.slot) for e in entries]
     self.cache.extend([(e.slot, len(e.tokens)) for e in entries])
-    return pack_step(entries, lengths, [g.tables for g in self.cache.groups],
-                     self.cache.page_size, self.ops, self.device)
+    ctx = pack_step(entries, lengths, [g.tables for g in self.cache.groups],
+                    self.cache.page_size, self.ops, self.device)
+    ctx.older_keys_settled = True  # what the cache holds below a request's length comes from earlier steps
+    return ctx
 
   # ---- generation -------------------------------------------------------------
   def add_request(self, prompt: Sequence[int], params: SamplingParams | None = None,

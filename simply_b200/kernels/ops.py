@@ -187,7 +187,7 @@ class CudaOps:
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
                          c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_int,
-                         c_void, c_void, c_int, c_void, c_void, c_void]
+                         c_void, c_void, c_int, c_void, c_int, c_void, c_void]
       decode.restype = c_int
       make_map = getattr(lib, f"sb_attn_tensor_map_hd{head_dim}")
       make_map.argtypes = [c_void, c_void, ctypes.c_longlong, c_int]
@@ -546,7 +546,8 @@ class CudaOps:
                     plan["num_decode"], plan["chunk"], _ptr(part_o), _ptr(part_ml), _ptr(self._attn_counter),
                     plan["rows_max"],
                     _ptr(plan["split_start"]), _ptr(plan["split_count"]), self.decode_variant,
-                    self._tensor_map(storage, head_dim, ctx.page_size), _ptr(self.err), self._stream())
+                    self._tensor_map(storage, head_dim, ctx.page_size),
+                    int(getattr(ctx, "older_keys_settled", False)), _ptr(self.err), self._stream())
         self.launches += 2
         if rc:
           raise KernelError(f"sb_attn_decode: {_STATUS.get(rc, rc)}")
