@@ -29,9 +29,17 @@ from simply_b200.parts.attention import PagedAttention
 
 
 def graphable(model: Any) -> bool:
-  """Graphs are used when every mixer is the built-in paged attention (other mixers may
-  read host-side metadata that a replay does not refresh)."""
-  return all(type(b.mixer) is PagedAttention for b in model.blocks.values())
+  """Graphs are used when every layer is made of the package's own parts: a foreign mixer,
+  feed-forward, block or position encoding may read host-side metadata that a replay does not
+  refresh, or synchronise with the host, which a capture forbids."""
+  from simply_b200.parts.block import PreNormBlock, SandwichNormBlock
+  from simply_b200.parts.feedforward import GatedFeedForward
+  from simply_b200.parts.position import NoPositionEncoding, RotaryEncoding
+
+  return all(
+      type(b) in (SandwichNormBlock, PreNormBlock) and type(b.mixer) is PagedAttention
+      and type(b.mixer.position) in (RotaryEncoding, NoPositionEncoding)
+      and type(b.feed_forward) is GatedFeedForward for b in model.blocks.values())
 
 
 @dataclasses.dataclass

@@ -270,7 +270,9 @@ class CudaOps:
     """TMA descriptor of a cache storage (made once per storage), or None where TMA cannot be used."""
     if head_dim % 64 or page_size & (page_size - 1):
       return None
-    key = (storage.data_ptr(), head_dim, page_size)
+    # The descriptor holds the storage's address and its number of rows (rows beyond read as
+    # zeros): another storage that the allocator puts at the same address must not find it.
+    key = (storage.data_ptr(), storage.numel(), head_dim, page_size)
     buf = self._tensor_maps.get(key)
     if buf is None:
       make_map = self._attention_lib(head_dim)[2]
