@@ -388,6 +388,29 @@ def test_tcgen05_prefill_long_walks(table, hq, hkv, dh, ps, window, cap):
     close(got, want, dtype, 2.0)
 
 
+def test_a_cache_at_a_reused_address_gets_a_descriptor_of_its_own(table):
+  """The decode kernels read the cache through a TMA descriptor that the kernel table keeps per
+  storage.  A second, larger storage at the same address (another engine after the first one was
+  freed) must not get the first one's descriptor: its rows would end too early and the keys of
+  the higher pages would read as zeros."""
+  dtype = torch.bfloat16
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  hq, hkv, dh, ps = 4, 2, 64, 16
+  arena = torch.zeros(8 * 1024 * 1024, dtype=dtype, device="cuda")
+  for seqs in ([(40, 1)], [(900, 1), (500, 1), (30, 1)]):  # the second cache has many more pages
+    sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=None, page_size=ps, dtype=dtype,
+                       device="cuda", ops=ops, seed=4)
+    at_same_address = arena[:sc.storage.numel()].view_as(sc.storage)
+    at_same_address.copy_(sc.storage)
+    assert at_same_address.data_ptr() == arena.data_ptr()
+    q = torch.randn(sc.ctx.num_tokens, hq, dh).to(dtype).cuda()
+    want = run_attention(ref, q, sc, hq, hkv, dh, 30.0, None)
+    got = ops.paged_attention(q, at_same_address, sc.block_table, sc.ctx, num_heads=hq, num_kv_heads=hkv,
+                              head_dim=dh, logit_softcap=30.0, window=None)
+    ops.check_errors()
+    close(got, want, dtype, 2.0)
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("ps", [16, 64])
 @pytest.mark.parametrize("window", [None, 96])
