@@ -216,6 +216,11 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     if (lane == 0) {
       const uint32_t idesc_qk = idesc_bf16_f32(BM, BN, false, false);
       bool ok = (QS_SLABS == 0 || mbar_wait_bounded(&q_full, 0)) && (QT_DIMS == 0 || mbar_wait_bounded(&qt_ready, 0));
+      // Descriptors are a base plus a constant per step of 16 dims (the start address is the
+      // descriptor's low field, in units of 16 bytes), so that between two products of a tile
+      // this thread has one addition to do: it is the thread the whole block waits for.
+      const uint64_t q_desc0 = smem_desc_sw128(sq, 16, 1024);
+      const uint64_t k_desc0 = smem_desc_sw128(sk, 16, 1024);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % K_STAGES;
         if (!mbar_wait_bounded(&k_full[s], (j / K_STAGES) & 1) ||
@@ -224,16 +229,17 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           break;
         }
         tc_fence_after_sync();
+        const uint64_t k_desc = k_desc0 + (uint64_t)((s * KV_TILE_BYTES) >> 4);
+        const uint32_t s_tmem = tmem + S_COL0 + (j % S_BUFS) * BN;
 #pragma unroll
         for (int ks = 0; ks < DH / 16; ++ks) {
-          const uint64_t bdesc = smem_desc_sw128(sk + s * KV_TILE_BYTES + (ks / 4) * (BN * 128) + (ks % 4) * 32, 16, 1024);
+          const uint64_t bdesc = k_desc + (uint64_t)(((ks / 4) * (BN * 128) + (ks % 4) * 32) >> 4);
           if (ks < QT_DIMS / 16) {
             // 16 dims of Q are 8 columns of two bfloat16 each
-            tc_mma_f16_ts(tmem + S_COL0 + (j % S_BUFS) * BN, tmem + QT_COL0 + ks * 8, bdesc, idesc_qk, ks > 0);
+            tc_mma_f16_ts(s_tmem, tmem + QT_COL0 + ks * 8, bdesc, idesc_qk, ks > 0);
           } else {
             const int kq = ks - QT_DIMS / 16;
-            const uint64_t a = smem_desc_sw128(sq + (kq / 4) * (BM * 128) + (kq % 4) * 32, 16, 1024);
-            tc_mma_f16(tmem + S_COL0 + (j % S_BUFS) * BN, a, bdesc, idesc_qk, ks > 0);
+            tc_mma_f16(s_tmem, q_desc0 + (uint64_t)(((kq / 4) * (BM * 128) + (kq % 4) * 32) >> 4), bdesc, idesc_qk, ks > 0);
           }
         }
         tc_commit(&s_full[j % (2 * S_BUFS)]);  // also frees the key tile's stage
@@ -244,6 +250,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     // ---- MMA issue of O += P.V (one thread) ---------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc_pv = idesc_bf16_f32(BM, DH, false, true);  // V: the N index (dims) is contiguous
+      const uint64_t v_desc0 = smem_desc_sw128(sv, BN * 128, 1024);
       bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % V_STAGES;
@@ -259,7 +266,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           // P comes from tensor memory, where it overwrote the tile's S: 16 keys are 8 columns of
           // two bfloat16 each.  16 keys further in V = 16 rows of 128 bytes; the next 64 dims are
           // one slab (BN * 128 bytes) further.
-          const uint64_t bdesc = smem_desc_sw128(sv + s * KV_TILE_BYTES + kk * 16 * 128, BN * 128, 1024);
+          const uint64_t bdesc = v_desc0 + (uint64_t)((s * KV_TILE_BYTES + kk * 16 * 128) >> 4);
           tc_mma_f16_ts(tmem + O_COL0, tmem + S_COL0 + (j % S_BUFS) * BN + kk * 8, bdesc, idesc_pv, j > 0 || kk > 0);
         }
         tc_commit(&pv_done[j % S_BUFS]);  // also frees the value tile's stage
