@@ -132,6 +132,35 @@ def test_preemption_gives_the_same_tokens(folders):
   assert tight_engine.cache.min_free_pages() == tight_engine.cache.num_pages
 
 
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_random_workloads_float32_equal_plain(folders, seed):
+  """Random mixes of what the host side of decoding can meet: page sizes, bursts of several steps,
+  small token budgets, pools so small that requests are preempted, requests of unequal length that
+  finish at different steps (so that graphs of several batch sizes are used and resumed).  Every
+  token must be the plain model's."""
+  rng = np.random.default_rng(100 + seed)
+  which = "ab"[seed % 2]
+  plain = PlainGemma2(folders[which])
+  lengths = [int(n) for n in rng.integers(1, 60, size=int(rng.integers(3, 7)))]
+  steps = [int(n) for n in rng.integers(1, 40, size=len(lengths))]
+  prompts = prompts_for(plain, lengths, seed=50 + seed)
+  sampled = seed >= 2
+  params = [SamplingParams(temperature=0.7 if sampled else 0.0, seed=seed * 10 + i, max_decode_steps=n, stop_token_ids=())
+            for i, n in enumerate(steps)]
+  want = [plain.sample(p, n, 0.7, seed * 10 + i) if sampled else plain.greedy(p, n)
+          for i, (p, n) in enumerate(zip(prompts, steps))]
+  page = int(rng.choice([4, 8, 16]))
+  longest = max(l + n for l, n in zip(lengths, steps))
+  eng = engine_for(folders[which], "float32", page_size=page, batch_size=int(rng.integers(2, 5)),
+                   intermediate_steps=int(rng.choice([1, 3, 8])), max_num_issue_tokens=int(rng.choice([5, 16, 64])),
+                   max_cache_tokens=int(-(-longest // page) * page * rng.choice([1.5, 2.5, 4.0])) + 2 * page)
+  got = eng.generate(prompts, params)
+  eng.ops.check_errors()
+  assert [r.output_token_ids for r in got] == want
+  eng.cache.check_invariants()
+  assert eng.cache.min_free_pages() == eng.cache.num_pages
+
+
 def test_engine_refuses_without_cuda_kernels(monkeypatch):
   from simply_b200.kernels import ops as ops_mod
   monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
