@@ -25,6 +25,16 @@ def models(tmp_path_factory):
     requests = cases.make_requests(which, plain.cfg["vocab_size"])
     expected = {rid: plain.forward(toks) for rid, toks in requests.items()}
     out[which] = (folder, plain.cfg["vocab_size"], requests, expected)
+  # The same two with head sizes of 64 and 128 and groups that divide 128: these sizes take the
+  # kernels that the large configurations take (tcgen05 prefill attention, decode attention fed by
+  # TMA), which head sizes of 16 and 32 do not.
+  wide = {"a": dict(head_dim=64), "b": dict(head_dim=128, num_attention_heads=4, num_key_value_heads=2)}
+  for which, changes in wide.items():
+    folder = write_tiny(which, root / "wide", "bfloat16", **changes)
+    plain = PlainGemma2(folder)
+    requests = cases.make_requests(which, plain.cfg["vocab_size"])
+    expected = {rid: plain.forward(toks) for rid, toks in requests.items()}
+    out[which + "_wide"] = (folder, plain.cfg["vocab_size"], requests, expected)
   return out
 
 
@@ -36,6 +46,15 @@ def test_trace_run_four_ways(models, tmp_path, which, dtype):
   out_dir = str(tmp_path / "out")
   trace_util.run_tool(folder, dtype, steps, out_dir, trace_util.tokens_needed(steps, 64))
   cases.compare(trace_util.collect(steps, out_dir, vocab), requests, expected, dtype)
+
+
+@pytest.mark.parametrize("which", ["a_wide", "b_wide"])
+def test_trace_run_four_ways_with_the_large_models_kernels(models, tmp_path, which):
+  folder, vocab, requests, expected = models[which]
+  steps = cases.combined_trace(requests)
+  out_dir = str(tmp_path / "out")
+  trace_util.run_tool(folder, "bfloat16", steps, out_dir, trace_util.tokens_needed(steps, 64))
+  cases.compare(trace_util.collect(steps, out_dir, vocab), requests, expected, "bfloat16")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
