@@ -232,6 +232,7 @@ def main(argv=None):
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--context", type=int, default=0, help="0: the preset's max_position_embeddings")
   ap.add_argument("--layers", type=int, default=0, help="0: all layers of the preset")
+  ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
   ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
   ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                   help="run ONE eager step of this kind between cudaProfilerStart/Stop and exit "
@@ -262,7 +263,7 @@ def main(argv=None):
   context = args.context or cfg.max_position_embeddings
   max_batch = 8 if args.skip_points else 64
   max_batch = max(max_batch, args.batch)
-  ec = EngineConfig(activation_dtype="bfloat16", page_size=64, batch_size=max_batch, max_seq_len=context,
+  ec = EngineConfig(activation_dtype="bfloat16", page_size=args.page_size, batch_size=max_batch, max_seq_len=context,
                     max_cache_tokens=max_batch * context, max_num_issue_tokens=2048, intermediate_steps=1)
   t0 = time.time()
   engine = Engine.from_config(cfg, seed=0, engine_config=ec, matrix_std=0.02, scale_std=0.0)
@@ -356,7 +357,7 @@ def main(argv=None):
           "model": args.preset, "layers": layers, "layers_full": full_layers, "width": cfg.hidden_size,
           "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
           "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size, "window": cfg.sliding_window,
-          "global_batch": args.batch, "seq_len": context, "page_size": 64, "parallelism": "1 GPU",
+          "global_batch": args.batch, "seq_len": context, "page_size": args.page_size, "parallelism": "1 GPU",
           "l2": "inputs larger than L2", "peaks": peaks_from, "params": n["params"],
       },
       "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,

@@ -48,7 +48,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
                                T* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
                                int head_dim, int page_size, int num_pages, float cap, int window,
                                int* err) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   extern __shared__ float smem[];  // per warp: head_dim floats of q
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

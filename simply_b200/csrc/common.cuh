@@ -122,6 +122,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // is always correct on its own.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The same for a whole block, at a point all its threads reach: one thread waits, the others
+// stand at the block's barrier.  (Thousands of threads each waiting out a long kernel before
+// them slowed that kernel down: a norm of 8 rows, launched early behind a 60 us product, cost
+// 50 us; with one waiting thread per block it costs nothing.)
+__device__ __forceinline__ void pdl_wait_block() {
+  if (threadIdx.x == 0) pdl_wait();
+  __syncthreads();
+}
 
 #include <stdlib.h>
 

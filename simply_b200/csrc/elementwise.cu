@@ -16,7 +16,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float scale,
                              float* __restrict__ out, int width, int vocab, int* err) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   int id = ids[t];
@@ -83,7 +83,7 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
     if (branch && w_post) load_scalars<N>(w_post, post_f32, threadIdx.x * N, wp);
     if (w_pre) load_scalars<N>(w_pre, pre_f32, threadIdx.x * N, wq);
   }
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   int src = rows ? rows[r] : r;
   if (src < 0 || src >= num_rows_total) {
@@ -259,7 +259,7 @@ extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const v
 template <typename Tin, typename Tout>
 __global__ void rms_norm_kernel(const Tin* __restrict__ x, const void* __restrict__ w, int w_f32, float eps,
                                 int plus_one, Tout* __restrict__ y, int width) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   extern __shared__ float row[];
   float* scratch = row + width;
@@ -305,7 +305,7 @@ extern "C" int sb_rms_norm(const void* x, int in_dtype, const void* w, int w_f32
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out,
                                    int width, int num_rows_total, int* err) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   int src = rows[blockIdx.x];
   if (src < 0 || src >= num_rows_total) {
@@ -331,7 +331,7 @@ extern "C" int sb_gather_rows(const void* x, int dtype, const int* rows, void* o
 
 template <typename T>
 __global__ void add_to_residual_kernel(float* __restrict__ h, const T* __restrict__ x, size_t n) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) h[i] += to_f32<T>(x[i]);
@@ -350,7 +350,7 @@ extern "C" int sb_add_to_residual(float* h, const void* x, int dtype, long long 
 
 template <typename Tin, typename Tout>
 __global__ void cast_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, size_t n) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = from_f32<Tout>(to_f32<Tin>(x[i]));
@@ -376,7 +376,7 @@ extern "C" int sb_cast(const void* x, int in_dtype, void* y, int out_dtype, long
 __global__ void rotation_tables_kernel(const int* __restrict__ positions, const float* __restrict__ timescale,
                                        float scale_factor, float* __restrict__ cos_out,
                                        float* __restrict__ sin_out, int num_tokens, int half) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= num_tokens * half) return;
@@ -414,7 +414,7 @@ __global__ void rope_cache_write_kernel(const T* __restrict__ qkv, const float* 
                                         int max_pages, const int* __restrict__ token_seq,
                                         const int* __restrict__ positions, int num_q_heads, int num_kv_proj,
                                         int head_dim, int page_size, int num_pages, int write_cache, int* err) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int half = head_dim / 2;
@@ -532,7 +532,7 @@ __device__ __forceinline__ float apply_activation(float g, int act) {
 template <typename T>
 __global__ void gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden,
                                             int act, size_t chunks) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   constexpr int N = Vec<T>::N;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -550,7 +550,7 @@ __global__ void gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden, int act,
                                         size_t n) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -589,7 +589,7 @@ extern "C" int sb_gated_activation(const void* gate_up, int dtype, void* z, int 
 // Soft cap in place on float32 logits: x = cap * tanh(x / cap).  simply/model_lib.py:107-109.
 // ---------------------------------------------------------------------------
 __global__ void soft_cap_kernel(float* __restrict__ x, float cap, size_t n) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] = cap * tanhf(x[i] / cap);
@@ -613,7 +613,7 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       int* __restrict__ positions, int* __restrict__ q_start,
                                       int* __restrict__ sample_params, int* __restrict__ history,
                                       int* __restrict__ step_counter, int batch) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *step_counter;

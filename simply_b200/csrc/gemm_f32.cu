@@ -14,7 +14,7 @@ __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restric
                                                           const float* __restrict__ w,
                                                           float* __restrict__ out, int M, int N, int K,
                                                           float cap) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];

@@ -115,7 +115,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
     }
   };
   load_weights(wa, warp);
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   for (int s0 = warp; s0 < steps; s0 += STRIDE) {
     uint4 xv[UNROLL][MT];
@@ -224,6 +224,23 @@ static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, 
                          int act, cudaStream_t stream, const RopeStore& rs = RopeStore{}) {
   const int n_out = epilogue == 2 ? N / 2 : N;
   const unsigned blocks = epilogue == 3 ? (unsigned)(N / 32) : (unsigned)((n_out + 15) / 16);
+  // Every block reads all of x through L1 just before it multiplies, so the stream of weights
+  // stands still for the length of an L2 access whenever x is not there.  Attention kernels leave
+  // the SMs split in favour of shared memory, and a kernel launched programmatically behind them
+  // inherits that split (nothing drains the SMs in between): ask for no more shared memory than
+  // the resident blocks' partial sums need, and so for the largest L1 beside it.
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    constexpr int SETS_MAX = 2;
+    constexpr int resident = 512 / (WARPS * 32) > 0 ? 512 / (WARPS * 32) : 1;
+    constexpr int needed = resident * (int)(sizeof(float) * WARPS * SETS_MAX * MT * 16 * 8 + 1024);
+    const int percent = min(100, needed * 100 / (227 * 1024) + 1);
+    cudaFuncSetAttribute(skinny_gemm_kernel<MT, WARPS, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+    cudaFuncSetAttribute(skinny_gemm_kernel<MT, WARPS, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+    cudaFuncSetAttribute(skinny_gemm_kernel<MT, WARPS, 2>, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+    cudaFuncSetAttribute(skinny_gemm_kernel<MT, WARPS, 3>, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+    carveout_set = true;
+  }
   if (epilogue == 0)
     sb_launch_early(skinny_gemm_kernel<MT, WARPS, 0>, blocks, WARPS * 32, 0, stream, x, w, out, M, N, K, cap,
         act, rs);

@@ -107,7 +107,7 @@ __device__ float block_max(float v, float* scratch) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_threshold_kernel(const float* __restrict__ logits, const int* __restrict__ params,
                         uint32_t* __restrict__ thresholds, int vocab) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   __shared__ float fscratch[33];
   const int r = blockIdx.x;
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(SLICE_THREADS)
 sample_slice_kernel(const float* __restrict__ logits, const int* __restrict__ params,
                     const uint32_t* __restrict__ thresholds, ArgMax* __restrict__ partial, int vocab,
                     int slice_len) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   __shared__ ArgMax ascratch[33];
   const int r = blockIdx.y, slice = blockIdx.x;
@@ -204,7 +204,7 @@ sample_slice_kernel(const float* __restrict__ logits, const int* __restrict__ pa
 }
 
 __global__ void sample_final_kernel(const ArgMax* __restrict__ partial, int* __restrict__ out, int slices) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int r = blockIdx.x, lane = threadIdx.x;
   ArgMax best{-FLT_MAX, 0x7fffffff};
