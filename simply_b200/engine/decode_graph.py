@@ -17,6 +17,7 @@ of the whole burst; chunks with nothing visible at a given step come out empty.
 
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 import gc
 from typing import Any, Sequence
@@ -25,6 +26,7 @@ import numpy as np
 import torch
 
 from simply_b200.engine.batch import StepContext
+from simply_b200.kernels.ops import KernelError
 from simply_b200.parts.attention import PagedAttention
 
 
@@ -59,6 +61,8 @@ class _Graph:
   chunks: dict
   launches: int
   resume: dict | None = None  # what the device holds after the last burst (see DecodeRunner.run)
+  graph_exec: Any = None  # the instantiated graph's handle and the buffers' addresses, for the native launch
+  pointers: tuple = ()
 
 
 class DecodeRunner:
@@ -77,6 +81,7 @@ class DecodeRunner:
     self.attn_kinds = sorted(kinds, key=lambda k: (k[0] or 0, k[1]))
     self.attn_shapes = kinds
     self.stream = torch.cuda.Stream(device=engine.device)
+    self._stream_ptr = ctypes.c_void_p(self.stream.cuda_stream)
     self.h2d_bytes = 0  # bytes copied to and from the device by `run` so far
     self.d2h_bytes = 0
 
@@ -194,6 +199,14 @@ class DecodeRunner:
     put("step_counter", [0])
 
   # ---- running -----------------------------------------------------------------------
+  def _chunk_ranges(self, g, lengths: np.ndarray, steps: int) -> list:
+    return [self.ops.decode_chunk_range(lengths, steps, window, plan["chunk"])
+            for (window, _), plan in g.plans.items()]
+
+  @staticmethod
+  def _same_ranges(a: list, b: list) -> bool:
+    return all(np.array_equal(x[0], y[0]) and np.array_equal(x[1], y[1]) for x, y in zip(a, b))
+
   def run(self, slots: Sequence[int], last_tokens: Sequence[int], sample_params: np.ndarray,
           steps: int) -> np.ndarray:
     """Decodes `steps` tokens for every slot; returns the sampled tokens [steps, batch].
@@ -222,15 +235,18 @@ class DecodeRunner:
     slots_t = tuple(int(s) for s in slots)
     last_tokens = np.asarray(last_tokens, dtype=np.int32)
     sample_params = np.asarray(sample_params, dtype=np.int32).reshape(batch, 6)
-    ranges = [self.ops.decode_chunk_range(lengths, steps, window, plan["chunk"])
-              for (window, _), plan in g.plans.items()]
     version = cache.tables_version()
     r = g.resume
-    resumed = (
+    follows = (
         r is not None and g.captured and r["slots"] == slots_t and r["version"] == version
         and r["counter"] + steps <= self.MAX_BURST and np.array_equal(r["lengths"], lengths)
-        and np.array_equal(r["params"], sample_params)
-        and all(np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]) for a, b in zip(r["ranges"], ranges)))
+        and np.array_equal(r["params"], sample_params))
+    if follows and r["next_steps"] == steps:
+      # The last burst worked out, while the device ran, what a burst like itself would need next.
+      ranges, resumed = r["next_ranges"], r["next_ranges_same"]
+    else:
+      ranges = self._chunk_ranges(g, lengths, steps)
+      resumed = follows and self._same_ranges(r["ranges"], ranges)
     first_row = r["counter"] if resumed else 0
     h = g.host.numpy()
 
@@ -253,34 +269,46 @@ class DecodeRunner:
         put(f"items{window}_{group}", items)
         put(f"split_start{window}_{group}", start)
         put(f"split_count{window}_{group}", count)
-    # Copy, replays and read-back run on the runner's own stream, the one the graph was captured on.
-    self.stream.wait_stream(torch.cuda.current_stream(eng.device))
-    with torch.cuda.stream(self.stream):
-      if resumed:
-        o, n = g.views["token_ids"]
-        g.meta[o:o + n].copy_(g.host[o:o + n], non_blocking=True)
-        self.h2d_bytes += 4 * n
-      else:
+    # Copy, replays and read-back run on the runner's own stream, the one the graph was captured
+    # on, issued by one native call.  (A burst that goes on from the last one needs no order with
+    # the engine's stream: nothing ran there for these requests since, or their lengths would differ.)
+    if not resumed:
+      self.stream.wait_stream(torch.cuda.current_stream(eng.device))
+    replays = steps
+    o, n = g.views["token_ids"] if resumed else (0, g.meta.numel())
+    if not g.captured:
+      with torch.cuda.stream(self.stream):
         g.meta.copy_(g.host, non_blocking=True)
-        self.h2d_bytes += 4 * g.meta.numel()
-      self.d2h_bytes += 4 * steps * batch
-      replays = steps
-      if not g.captured:
         self._first_step_and_capture(g)
-        replays -= 1
-      for _ in range(replays):
-        g.graph.replay()
-      rows = slice(first_row, first_row + steps)
-      g.host_history[rows].copy_(g.history[rows], non_blocking=True)
-      self.stream.synchronize()
-    out = g.host_history[rows].numpy().copy()
-    # The state the device is in now, as the next burst would have to describe it.
+      g.graph_exec = ctypes.c_void_p(g.graph.raw_cuda_graph_exec())
+      g.pointers = (g.meta.data_ptr(), g.host.data_ptr(), g.history.data_ptr(), g.host_history.data_ptr())
+      replays -= 1
+      self.h2d_bytes += 4 * n
+      n = 0  # already there
+    meta_p, host_p, history_p, host_history_p = g.pointers
+    row_bytes = 4 * batch
+    rows = slice(first_row, first_row + steps)
+    rc = self.ops.lib.sb_graph_burst(
+        g.graph_exec, ctypes.c_void_p(meta_p + 4 * o), ctypes.c_void_p(host_p + 4 * o), 4 * n, replays,
+        ctypes.c_void_p(host_history_p + first_row * row_bytes), ctypes.c_void_p(history_p + first_row * row_bytes),
+        steps * row_bytes, self._stream_ptr)
+    if rc != 0:
+      raise KernelError(f"decode burst: CUDA error {rc}")
+    self.h2d_bytes += 4 * n
+    self.d2h_bytes += steps * row_bytes
+    # While the device works: the state it will be in, as the next burst would have to describe
+    # it, and whether a burst of the same length could go on from it.
     next_params = sample_params.copy()
     next_params[:, 5] += steps
-    # (The chunk ranges are those of a burst of the same length from the new lengths; a burst of
-    # another length compares unequal or equal on its own merits.)
-    g.resume = dict(slots=slots_t, version=version, counter=first_row + steps, lengths=lengths + steps,
-                    params=next_params, ranges=ranges)
+    next_lengths = lengths + steps
+    next_ranges = self._chunk_ranges(g, next_lengths, steps)
+    g.resume = dict(slots=slots_t, version=version, counter=first_row + steps, lengths=next_lengths,
+                    params=next_params, ranges=ranges, next_steps=steps, next_ranges=next_ranges,
+                    next_ranges_same=self._same_ranges(ranges, next_ranges))
+    rc = self.ops.lib.sb_stream_wait(self._stream_ptr)
+    if rc != 0:
+      raise KernelError(f"decode burst: CUDA error {rc}")
+    out = g.host_history[rows].numpy().copy()
     self.ops.launches += g.launches * replays
     eng.num_steps += steps
     return out

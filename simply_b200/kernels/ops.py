@@ -136,6 +136,10 @@ class CudaOps:
       fn = getattr(self.lib, name)
       fn.argtypes = argtypes
       fn.restype = c_int
+    self.lib.sb_graph_burst.argtypes = [c_void, c_void, c_void, c_ll, c_int, c_void, c_void, c_ll, c_void]
+    self.lib.sb_graph_burst.restype = c_int
+    self.lib.sb_stream_wait.argtypes = [c_void]
+    self.lib.sb_stream_wait.restype = c_int
     self.lib.sb_sample_slices.argtypes = [c_int, c_int]
     self.lib.sb_sample_slices.restype = c_int
 
