@@ -82,8 +82,24 @@ class DecodeRunner:
     self.attn_shapes = kinds
     self.stream = torch.cuda.Stream(device=engine.device)
     self._stream_ptr = ctypes.c_void_p(self.stream.cuda_stream)
+    self.pool = torch.cuda.graph_pool_handle()
     self.h2d_bytes = 0  # bytes copied to and from the device by `run` so far
     self.d2h_bytes = 0
+
+  def batch_bucket(self, live: int) -> int:
+    """The batch size of the graph that serves `live` requests: 1, 2, 4, 8, then steps of 8 up
+    to 32, of 16 up to 64, of 32 beyond (the weight-streaming products cost the same for 1 to 8
+    and for 9 to 16 rows; attention and the output layer grow with the rows), never more than
+    the engine's slots unless `live` itself is."""
+    if live <= 8:
+      size = 1 << (live - 1).bit_length()
+    elif live <= 32:
+      size = -(-live // 8) * 8
+    elif live <= 64:
+      size = -(-live // 16) * 16
+    else:
+      size = -(-live // 32) * 32
+    return max(live, min(size, self.engine.cache.max_slots))
 
   # ---- layout of the static buffer -----------------------------------------------
   def _span(self, bucket: int, window: int | None) -> int:
@@ -176,8 +192,13 @@ class DecodeRunner:
       gc_was_on = gc.isenabled()
       gc.disable()
       try:
-        with torch.cuda.graph(g.graph, stream=self.stream):
+        # (Not through torch.cuda.graph(): it empties the allocator's caches first, which costs
+        # more than the capture.  All graphs share one pool: they never run at the same time.)
+        g.graph.capture_begin(pool=self.pool)
+        try:
           g.step_fn()
+        finally:
+          g.graph.capture_end()
       finally:
         if gc_was_on:
           gc.enable()
@@ -216,11 +237,23 @@ class DecodeRunner:
     """
     eng = self.engine
     cache = eng.cache
-    batch = len(slots)
+    live = len(slots)
     if not 1 <= steps <= self.MAX_BURST:
       raise ValueError(f"a decode burst has 1..{self.MAX_BURST} steps, got {steps}")
     lengths = np.array([cache.length(s) for s in slots], dtype=np.int64)
     cache.extend([(s, steps) for s in slots])
+    # Graphs exist for a few batch sizes only (a capture costs tens of milliseconds, and a batch
+    # that shrinks as requests end would need one per size).  The rows up to the next such size
+    # repeat the last request: they compute what it computes, store the same keys and values to
+    # the same places, and their tokens are dropped.
+    batch = self.batch_bucket(live)
+    if batch > live:
+      pad = batch - live
+      slots = list(slots) + [slots[-1]] * pad
+      last_tokens = list(last_tokens) + [last_tokens[-1]] * pad
+      sample_params = np.asarray(sample_params, dtype=np.int32).reshape(live, 6)
+      sample_params = np.concatenate([sample_params, np.repeat(sample_params[-1:], pad, axis=0)])
+      lengths = np.concatenate([lengths, np.repeat(lengths[-1:], pad)])
     bucket = 1024
     while bucket < int(lengths.max()) + steps:
       bucket *= 2
@@ -308,7 +341,7 @@ class DecodeRunner:
     rc = self.ops.lib.sb_stream_wait(self._stream_ptr)
     if rc != 0:
       raise KernelError(f"decode burst: CUDA error {rc}")
-    out = g.host_history[rows].numpy().copy()
+    out = g.host_history[rows].numpy()[:, :live].copy()
     self.ops.launches += g.launches * replays
     eng.num_steps += steps
     return out

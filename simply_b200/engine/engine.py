@@ -128,7 +128,12 @@ class Engine:
   def step_raw(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
     """Runs one batch; returns float32 logits [wanted, vocab] (None if nothing is wanted)."""
     ctx = self._prepare(entries)
-    logits = self.model.forward(ctx, self.caches)
+    hold = getattr(self.ops, "hold_stream", None)  # (a kernel table without streams has none)
+    if hold is None:
+      logits = self.model.forward(ctx, self.caches)
+    else:
+      with hold():
+        logits = self.model.forward(ctx, self.caches)
     self.num_steps += 1
     return logits
 

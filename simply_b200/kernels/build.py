@@ -143,7 +143,7 @@ def _build(srcs: list[str], lib_name: str, defines: list[str], verbose: bool, fo
         last = time.time()
   tmp = lib + f".{os.getpid()}.tmp"
   link = [nvcc, "-shared", "-o", tmp, *sorted(objs), "-gencode", "arch=compute_100a,code=sm_100a",
-          "-lcudart"]
+          "-lcudart", "-ldl"]
   r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
   if r.returncode != 0:
     raise KernelBuildError(f"linking {lib_name} failed:\n{r.stdout.decode(errors='replace')}")

@@ -61,6 +61,19 @@ class KernelError(RuntimeError):
   pass
 
 
+class _HeldStream:
+
+  def __init__(self, ops):
+    self.ops = ops
+
+  def __enter__(self):
+    self.previous = self.ops._step_stream
+    self.ops._step_stream = ctypes.c_void_p(torch.cuda.current_stream(self.ops.device).cuda_stream)
+
+  def __exit__(self, *exc):
+    self.ops._step_stream = self.previous
+
+
 class CudaOps:
 
   name = "cuda"
@@ -92,6 +105,9 @@ class CudaOps:
     self._decode_slots: dict[int, int] = {}
     # 0: the kernel is picked by the number of query rows; 1 forbids TMA; 16 forces the 16-row kernel (tests).
     self.decode_variant = 0
+    self.direct_library_products = True  # False: through torch.mm
+    self._library_workspaces: dict = {}
+    self._step_stream = None
     # 0: prefill tiles of 64 query rows; 64 or 128 forces a size.
     self.prefill_rows = 0
     # Prefill attention on the tcgen05 tensor cores where the shapes allow (head size a multiple of
@@ -136,6 +152,8 @@ class CudaOps:
       fn = getattr(self.lib, name)
       fn.argtypes = argtypes
       fn.restype = c_int
+    self.lib.sb_gemm_library_bf16.argtypes = [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_ll, c_void]
+    self.lib.sb_gemm_library_bf16.restype = c_int
     self.lib.sb_graph_burst.argtypes = [c_void, c_void, c_void, c_ll, c_int, c_void, c_void, c_ll, c_void]
     self.lib.sb_graph_burst.restype = c_int
     self.lib.sb_stream_wait.argtypes = [c_void]
@@ -144,7 +162,29 @@ class CudaOps:
     self.lib.sb_sample_slices.restype = c_int
 
   def _stream(self):
+    if self._step_stream is not None:
+      return self._step_stream
     return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+  def hold_stream(self):
+    """Context in which every launch goes to the stream that is current now, looked up once
+    instead of once per launch (an engine step is a few hundred launches)."""
+    return _HeldStream(self)
+
+  def _library_product(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """out = x . w^T through the matrix-product library with a kept algorithm; False when it
+    has none for this shape."""
+    stream = self._stream()
+    workspace = self._library_workspaces.get(stream.value)
+    if workspace is None:  # one per stream: products on different streams may run together
+      workspace = self._library_workspaces[stream.value] = torch.empty(32 << 20, dtype=torch.uint8, device=self.device)
+    m, k = x.shape
+    rc = self.lib.sb_gemm_library_bf16(_ptr(x), _ptr(w), _ptr(out), m, w.shape[0], k, int(out.dtype == torch.float32),
+                                       _ptr(workspace), workspace.numel(), stream)
+    if rc > 0:
+      raise KernelError(f"sb_gemm_library_bf16: cuBLAS status {rc}")
+    self.launches += rc == 0
+    return rc == 0
 
   def _call(self, name: str, *args) -> int:
     rc = getattr(self.lib, name)(*args, self._stream())
@@ -375,6 +415,10 @@ class CudaOps:
       out = self._new(m, n, dtype=torch.bfloat16)
       if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w), _ptr(out), m, n, k, 0, 0.0, 0, self.skinny_warps) == 0:
         return out
+    if self.direct_library_products and x.is_contiguous() and w.is_contiguous():
+      out = self._new(m, n, dtype=torch.bfloat16)
+      if self._library_product(x, w, out):
+        return out
     return torch.mm(x, w.t())
 
   def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, *, out_f32: bool = False, cap: float = 0.0,
@@ -411,6 +455,9 @@ class CudaOps:
     x = self.cast(x, torch.bfloat16)
     chunk = 32
     if r > chunk and k % 8 == 0:
+      if self.direct_library_products and x.is_contiguous() and self._library_product(x, table, out):
+        self._call("sb_soft_cap", _ptr(out), float(cap), out.numel())
+        return out
       try:
         torch.mm(x, table.t(), out_dtype=torch.float32, out=out)
         self._call("sb_soft_cap", _ptr(out), float(cap), out.numel())
