@@ -105,3 +105,21 @@ def test_the_package_has_no_cpu_path():
   from simply_b200.kernels.ops import CudaOps, KernelError
   with pytest.raises(KernelError, match="no CPU path"):
     CudaOps(torch.bfloat16)
+
+
+def test_decode_graph_batch_sizes():
+  """The batch sizes decode graphs are captured for: never below the live requests, few of them,
+  less than as many padded rows as live ones, at most half as many from 16 on, and not beyond the engine's slots."""
+  from types import SimpleNamespace
+  from simply_b200.engine.decode_graph import DecodeRunner
+
+  def bucket(live, slots):
+    fake = SimpleNamespace(engine=SimpleNamespace(cache=SimpleNamespace(max_slots=slots)))
+    return DecodeRunner.batch_bucket(fake, live)
+
+  sizes = {bucket(n, 256) for n in range(1, 257)}
+  assert len(sizes) <= 16
+  for n in range(1, 257):
+    b = bucket(n, 256)
+    assert n <= b <= max(2 * n - 1, 1) and (n < 16 or b <= n * 3 // 2)
+  assert bucket(37, 40) == 40 and bucket(41, 40) == 41 and bucket(5, 6) == 6
