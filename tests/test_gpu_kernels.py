@@ -220,6 +220,28 @@ def test_linear_bfloat16(table, m, n, k):
   close(ops.linear(x.cuda(), w.cuda()), ref.linear(x, w), torch.bfloat16)
 
 
+@pytest.mark.parametrize("m", [33, 64, 65, 100, 700, 2048])
+def test_library_product_is_called_directly(table, m):
+  """Steps of more than 32 tokens: the library product, called by the package's own code with an
+  algorithm kept per size class (one launch counted, no tensor-library call), gives what the
+  tensor library's call gives, whichever row count of a class comes first."""
+  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
+  n, k = 2304, 2048
+  x = torch.randn(m, k).to(torch.bfloat16)
+  w = (torch.randn(n, k) / k ** 0.5).to(torch.bfloat16)
+  before = ops.launches
+  got = ops.linear(x.cuda(), w.cuda())
+  assert ops.launches == before + 1
+  close(got, ref.linear(x, w), torch.bfloat16)
+  ops.direct_library_products = False
+  try:
+    through_torch = ops.linear(x.cuda(), w.cuda())
+    assert ops.launches == before + 1  # not one of the package's launches
+  finally:
+    ops.direct_library_products = True
+  close(got, through_torch.cpu(), torch.bfloat16)
+
+
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 64, 128), (200, 1000, 2304), (2048, 2304, 2048), (64, 4096, 328),
                                    (5, 70, 72)])
@@ -246,7 +268,8 @@ def test_gated_linear(table, m, f, k, act):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("r,v,k,cap", [(1, 1000, 96, 10.0), (7, 256, 64, 30.0), (45, 1003, 72, 0.0), (3, 25600, 2304, 30.0)])
+@pytest.mark.parametrize("r,v,k,cap", [(1, 1000, 96, 10.0), (7, 256, 64, 30.0), (45, 1003, 72, 0.0), (3, 25600, 2304, 30.0),
+                                       (40, 2048, 72, 30.0)])
 def test_lm_head(table, dtype, r, v, k, cap):
   ops, ref = table[dtype], ReferenceOps(dtype)
   x = (torch.randn(r, k) * 2).to(dtype)
