@@ -7,7 +7,8 @@ sequence ending at the full context (8,192 cached tokens), timed on the device o
 decode steps that run back to back from CUDA graphs.  `e2e` is the same through the
 public entry point (`Engine.add_request` / `Engine.step`), host tokens in and out, one
 host round trip per step.  `prefill` is one 2,048-token prompt in one step; `points`
-holds decode at batch 1 and 64; `roofline` relates the decode step's bytes (every weight
+holds decode at batch 1 and 64 and a serving-like run through `Engine.generate` (128
+requests over 64 slots, prompts of about 512 and outputs of about 128 tokens); `roofline` relates the decode step's bytes (every weight
 once, plus the cache of the live requests) to the measured copy bandwidth.
 
 A step reads 5.2 GB of weights and 0.65 GB of cache per sequence, far more than the
@@ -181,6 +182,33 @@ def time_decode(engine, torch, batch, context, steps, warmup, seed):
   return ms, launches
 
 
+def time_serving(engine, torch, cfg, requests=128, prompt=512, out=128):
+  """A serving-like run through `Engine.generate`, host tokens in and out: `requests` greedy
+  requests with prompts of prompt/2 to 3*prompt/2 tokens and out/2 to 3*out/2 generated tokens,
+  batched continuously over the engine's slots (prompt portions beside decoding requests, decode
+  steps from graphs).  Run twice; the second run, whose graphs exist, is the one reported."""
+  import numpy as np
+  from simply_b200 import SamplingParams
+
+  rng = np.random.default_rng(7)
+  result = {}
+  for _ in range(2):
+    prompts = [rng.integers(0, cfg.vocab_size, int(k)).tolist() for k in rng.integers(prompt // 2, prompt * 3 // 2, requests)]
+    params = [SamplingParams(temperature=0.0, max_decode_steps=int(k), stop_token_ids=())
+              for k in rng.integers(out // 2, out * 3 // 2, requests)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    results = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    tokens_in = sum(len(p) for p in prompts)
+    tokens_out = sum(len(r.output_token_ids) for r in results)
+    result = {"serve_requests": requests, "serve_prompt_tokens": tokens_in, "serve_output_tokens": tokens_out,
+              "serve_seconds": round(seconds, 3), "serve_output_tok_s": round(tokens_out / seconds, 1),
+              "serve_total_tok_s": round((tokens_in + tokens_out) / seconds, 1)}
+  return result
+
+
 def profile_step(engine, torch, cfg, args, context):
   """One eager step for a profiler.  The cache is made to *hold* the context without
   computing it (attention time does not depend on the cache's contents), so that few
@@ -334,6 +362,12 @@ def main(argv=None):
   while engine.has_unfinished():
     engine.step()
   e2e_value = args.batch * e2e_steps / e2e_s
+
+  if not args.skip_points:
+    budget = engine.scheduler.max_num_issue_tokens
+    engine.scheduler.max_num_issue_tokens = 2048
+    points.update(time_serving(engine, torch, cfg))
+    engine.scheduler.max_num_issue_tokens = budget
 
   clocks = sampler.stop()
   step_bytes = decode_bytes(cfg, layers, args.batch, context)
