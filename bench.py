@@ -143,6 +143,15 @@ def reference_arm(args):
   return 0
 
 
+def settle(torch, seconds=0.5):
+  """Filling the cache for a measurement means tens of thousands of prompt tokens at full power,
+  after which the GPU runs under its power cap for some 50 ms (decode steps then take 2.5 instead
+  of 2.3 ms end to end).  Half a second of rest before the warm-up steps lets the clocks settle;
+  the clocks sampled during the run are in the output."""
+  torch.cuda.synchronize()
+  time.sleep(seconds)
+
+
 def time_decode(engine, torch, batch, context, steps, warmup, seed):
   """Device time of `steps` decode steps at `batch`, the last one ending at `context` cached
   tokens.  Returns (ms per step, kernel launches per step)."""
@@ -160,6 +169,7 @@ def time_decode(engine, torch, batch, context, steps, warmup, seed):
       n = min(chunk, start - done)
       engine.step_raw([StepEntry(slot, rng.integers(0, vocab, n).tolist(), ())])
       done += n
+  settle(torch)
   runner = engine._decode_runner
   params = engine.ops.pack_sample_params([0.0] * batch, [-1] * batch, [1.0] * batch, list(range(batch)),
                                          [start + 1] * batch)
@@ -307,6 +317,36 @@ def main(argv=None):
   # ---- decode, device-timed ----------------------------------------------------------
   ms_step, launches = time_decode(engine, torch, args.batch, context, args.steps, args.warmup, seed=1)
   value = args.batch / (ms_step * 1e-3)
+
+  # ---- end to end through the public entry point (next, while the GPU is in the same state) ---
+  rng = np.random.default_rng(4)
+  start = context - args.steps - args.warmup
+  prompts = [rng.integers(0, cfg.vocab_size, start).tolist() for _ in range(args.batch)]
+  sp = SamplingParams(temperature=0.0, max_decode_steps=args.steps + args.warmup, stop_token_ids=())
+  requests = [engine.add_request(p, sp) for p in prompts]
+  # All prompts in one step, so that every request starts to decode at the same step.
+  engine.scheduler.max_num_issue_tokens = args.batch * context
+  while any(not r.is_decoding for r in requests):
+    engine.step()  # prompt portions (untimed)
+  settle(torch)
+  for _ in range(args.warmup - 1):
+    engine.step()
+  torch.cuda.synchronize()
+  runner = engine._decode_runner
+  h2d0, d2h0 = runner.h2d_bytes, runner.d2h_bytes
+  t0 = time.perf_counter()
+  e2e_steps = 0
+  while engine.has_unfinished() and e2e_steps < args.steps:
+    engine.step()
+    e2e_steps += 1
+  torch.cuda.synchronize()
+  e2e_s = time.perf_counter() - t0
+  h2d = (runner.h2d_bytes - h2d0) // max(e2e_steps, 1)  # counted where the copies are made
+  d2h = (runner.d2h_bytes - d2h0) // max(e2e_steps, 1)
+  while engine.has_unfinished():
+    engine.step()
+  e2e_value = args.batch * e2e_steps / e2e_s
+
   points = {}
   if not args.skip_points:
     for b in (1, 64):
@@ -335,33 +375,6 @@ def main(argv=None):
   flops = prefill_flops(cfg, layers, p_tokens)
   prefill = {"value": round(p_tokens / (prefill_ms * 1e-3), 1), "tokens": p_tokens, "ms": round(prefill_ms, 3),
              "frac": round(flops / (prefill_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)}
-
-  # ---- end to end through the public entry point ------------------------------------------
-  start = context - args.steps - args.warmup
-  prompts = [rng.integers(0, cfg.vocab_size, start).tolist() for _ in range(args.batch)]
-  sp = SamplingParams(temperature=0.0, max_decode_steps=args.steps + args.warmup, stop_token_ids=())
-  requests = [engine.add_request(p, sp) for p in prompts]
-  # All prompts in one step, so that every request starts to decode at the same step.
-  engine.scheduler.max_num_issue_tokens = args.batch * context
-  while any(not r.is_decoding for r in requests):
-    engine.step()  # prompt portions (untimed)
-  for _ in range(args.warmup - 1):
-    engine.step()
-  torch.cuda.synchronize()
-  runner = engine._decode_runner
-  h2d0, d2h0 = runner.h2d_bytes, runner.d2h_bytes
-  t0 = time.perf_counter()
-  e2e_steps = 0
-  while engine.has_unfinished() and e2e_steps < args.steps:
-    engine.step()
-    e2e_steps += 1
-  torch.cuda.synchronize()
-  e2e_s = time.perf_counter() - t0
-  h2d = (runner.h2d_bytes - h2d0) // max(e2e_steps, 1)  # counted where the copies are made
-  d2h = (runner.d2h_bytes - d2h0) // max(e2e_steps, 1)
-  while engine.has_unfinished():
-    engine.step()
-  e2e_value = args.batch * e2e_steps / e2e_s
 
   if not args.skip_points:
     budget = engine.scheduler.max_num_issue_tokens
