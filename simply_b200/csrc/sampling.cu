@@ -182,7 +182,27 @@ sample_slice_kernel(const float* __restrict__ logits, const int* __restrict__ pa
   const int lo = slice * slice_len, hi = min(lo + slice_len, vocab);  // slice_len is a multiple of 4
   ArgMax best{-FLT_MAX, 0x7fffffff};
   if (temperature == 0.f || top_k == 1) {
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, ArgMax{row[i], i});
+    // Four entries per load where the row allows it (lo is a multiple of 4), two loads in flight.
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int hi4 = lo + (hi - lo) / 4 * 4;
+      ArgMax other{-FLT_MAX, 0x7fffffff};
+      int i = lo + threadIdx.x * 4;
+      for (; i + (int)blockDim.x * 4 < hi4; i += blockDim.x * 8) {
+        const float4 a = *reinterpret_cast<const float4*>(row + i);
+        const float4 b = *reinterpret_cast<const float4*>(row + i + blockDim.x * 4);
+        best = better(better(better(better(best, ArgMax{a.x, i}), ArgMax{a.y, i + 1}), ArgMax{a.z, i + 2}), ArgMax{a.w, i + 3});
+        const int j = i + blockDim.x * 4;
+        other = better(better(better(better(other, ArgMax{b.x, j}), ArgMax{b.y, j + 1}), ArgMax{b.z, j + 2}), ArgMax{b.w, j + 3});
+      }
+      for (; i < hi4; i += blockDim.x * 4) {
+        const float4 a = *reinterpret_cast<const float4*>(row + i);
+        best = better(better(better(better(best, ArgMax{a.x, i}), ArgMax{a.y, i + 1}), ArgMax{a.z, i + 2}), ArgMax{a.w, i + 3});
+      }
+      best = better(best, other);
+      for (int k = hi4 + threadIdx.x; k < hi; k += blockDim.x) best = better(best, ArgMax{row[k], k});
+    } else {
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, ArgMax{row[i], i});
+    }
   } else {
     const uint32_t threshold = thresholds[r];
     const uint32_t seed_lo = (uint32_t)p[3], seed_hi = (uint32_t)p[4], position = (uint32_t)p[5];
