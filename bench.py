@@ -360,6 +360,7 @@ def main(argv=None):
   p_tokens = min(2048, context)
   prompt = rng.integers(0, cfg.vocab_size, p_tokens).tolist()
   times = []
+  settle(torch)
   for i in range(3 + 5):
     slot = engine.open_request(f"prefill{i}")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
