@@ -227,7 +227,15 @@ def profile_step(engine, torch, cfg, args, context):
   from simply_b200 import StepEntry
 
   rng = np.random.default_rng(3)
-  if args.profile == "decode":
+  if args.profile == "mixed":
+    # A serving step: every other slot decodes one token at a context of a few hundred, beside
+    # the 600-token prompt of a request that has just been admitted.
+    slots = [engine.open_request(f"p{i}") for i in range(args.batch - 1)]
+    engine.cache.extend([(s, int(n)) for s, n in zip(slots, rng.integers(300, 900, len(slots)))])
+    new = engine.open_request("new")
+    entries = [StepEntry(s, [int(rng.integers(0, cfg.vocab_size))], (0,)) for s in slots]
+    entries.append(StepEntry(new, rng.integers(0, cfg.vocab_size, 600).tolist(), (599,)))
+  elif args.profile == "decode":
     slots = [engine.open_request(f"p{i}") for i in range(args.batch)]
     engine.cache.extend([(s, context - 2) for s in slots])
     entries = [StepEntry(s, [int(rng.integers(0, cfg.vocab_size))], (0,)) for s in slots]
@@ -241,7 +249,12 @@ def profile_step(engine, torch, cfg, args, context):
     engine.ops.sample(logits, [0.0] * len(entries), [-1] * len(entries), [1.0] * len(entries),
                       [0] * len(entries), [1] * len(entries))
 
-  if args.profile == "prefill":
+  if args.profile == "mixed":
+    step()  # warm-up; then the same step again with the prompt under a new request
+    engine.close_request(entries[-1].slot)
+    new = engine.open_request("new2")
+    entries = [StepEntry(e.slot, e.tokens, e.want) for e in entries[:-1]] + [StepEntry(new, entries[-1].tokens, entries[-1].want)]
+  elif args.profile == "prefill":
     step()  # warm-up on the same slot is not possible for a prompt; use a second request
     engine.close_request(entries[0].slot)
     slot = engine.open_request("p2")
@@ -272,7 +285,7 @@ def main(argv=None):
   ap.add_argument("--layers", type=int, default=0, help="0: all layers of the preset")
   ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
   ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
-  ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+  ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
                   help="run ONE eager step of this kind between cudaProfilerStart/Stop and exit "
                        "(for ncu --profile-from-start off); prints no benchmark line")
   args = ap.parse_args(argv)
