@@ -31,13 +31,38 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+def _find_number(tree, key):
+  """The number stored under `key` anywhere in a JSON tree (directly, or as {"value": number})."""
+  if isinstance(tree, dict):
+    if key in tree:
+      v = tree[key]
+      if isinstance(v, dict):
+        v = v.get("value")
+      if isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+        return float(v)
+    for child in tree.values():
+      found = _find_number(child, key)
+      if found is not None:
+        return found
+  elif isinstance(tree, list):
+    for child in tree:
+      found = _find_number(child, key)
+      if found is not None:
+        return found
+  return None
+
+
 def load_peaks():
   path = os.path.join(ROOT, "MEASURED_PEAKS.json")
   if os.path.isfile(path):
     try:
       with open(path) as f:
         d = json.load(f)
-      peaks = {k: float(d[k]) for k in FALLBACK_PEAKS if k in d}
+      peaks = {}
+      for k in FALLBACK_PEAKS:
+        v = _find_number(d, k)
+        if v is not None:
+          peaks[k] = v
       if "hbm_gbs" in peaks and "bf16_tflops" in peaks:
         peaks.setdefault("bf16_tflops_sustained", peaks["bf16_tflops"])
         return peaks, "measured"
