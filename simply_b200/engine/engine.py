@@ -200,7 +200,7 @@ class Engine:
     requests = [e.request for e in plan.entries]
     steps = max(1, min(self.engine_config.intermediate_steps, self._decode_runner.MAX_BURST))
     for r in requests:
-      steps = min(steps, r.params.max_decode_steps - len(r.output),
+      steps = min(steps, r.params.max_decode_steps - r.num_output,
                   self.engine_config.max_seq_len - len(r.tokens))
     steps = max(steps, 1)
     while steps > 1 and self.cache.pages_short([(r.slot, steps) for r in requests]):

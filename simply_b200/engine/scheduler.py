@@ -57,6 +57,10 @@ class Request:
     return self.tokens[len(self.prompt):]
 
   @property
+  def num_output(self) -> int:
+    return len(self.tokens) - len(self.prompt)
+
+  @property
   def remaining(self) -> int:
     return len(self.tokens) - self.num_cached
 
@@ -237,7 +241,7 @@ class Scheduler:
       stops = r.params.stop_token_ids if r.params.stop_token_ids is not None else self.eos_ids
       if token in stops:
         reason = "eos"
-      elif len(r.output) >= r.params.max_decode_steps:
+      elif r.num_output >= r.params.max_decode_steps:
         reason = "max_decode_steps"
       elif len(r.tokens) >= self.max_seq_len:
         reason = "max_seq_len"
