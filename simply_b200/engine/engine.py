@@ -213,9 +213,10 @@ class Engine:
                                      params, steps)
     finished: list[Request] = []
     for i in range(steps):
-      live = [e for e in plan.entries if e.request.status.value == "running"]
-      step_plan = StepPlan(live, [], [])
-      sampled = {e.request.request_id: int(tokens[i, requests.index(e.request)]) for e in live}
+      row = tokens[i].tolist()
+      live = [(j, e) for j, e in enumerate(plan.entries) if e.request.status.value == "running"]
+      step_plan = StepPlan([e for _, e in live], [], [])
+      sampled = {e.request.request_id: row[j] for j, e in live}
       finished += self.scheduler.commit(step_plan, sampled)
     # Requests that are still live hold exactly the tokens the burst cached.
     return finished

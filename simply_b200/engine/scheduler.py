@@ -39,7 +39,7 @@ class Status(enum.Enum):
   FINISHED = "finished"
 
 
-@dataclasses.dataclass
+@dataclasses.dataclass(eq=False)  # a request is itself: lists and queues look it up by identity
 class Request:
   request_id: object
   prompt: list[int]
