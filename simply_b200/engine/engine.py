@@ -140,9 +140,10 @@ class Engine:
   def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
     vocab = self.model.spec.vocab_size
     for e in entries:
-      for t in e.tokens:
-        if not 0 <= int(t) < vocab:
-          raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+      ids = np.asarray(e.tokens)
+      if ids.size and (ids.min() < 0 or ids.max() >= vocab):
+        bad = ids[(ids < 0) | (ids >= vocab)][0]
+        raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
     lengths = [self.cache.length(e.slot) for e in entries]
     self.cache.extend([(e.slot, len(e.tokens)) for e in entries])
     ctx = pack_step(entries, lengths, [g.tables for g in self.cache.groups],
