@@ -141,7 +141,10 @@ class Scheduler:
       return lo
 
     # 1. Decoding requests, oldest first.  Each must run; make room if needed.
-    decoding = sorted((r for r in self.running if r.is_decoding), key=lambda r: r.arrival)
+    decoding, in_prompt = [], []
+    for r in self.running:
+      (decoding if r.is_decoding else in_prompt).append(r)
+    decoding.sort(key=lambda r: r.arrival)
     if decoding and len(decoding) <= budget and self.cache.pages_short([(r.slot, 1) for r in decoding]) == 0:
       # The usual case, decided with one look at the pools: all of them fit, so each prefix does.
       for r in decoding:
@@ -170,7 +173,9 @@ class Scheduler:
       budget -= 1
 
     # 2. Prompt portions of live requests, oldest first.
-    for r in sorted((r for r in self.running if not r.is_decoding), key=lambda r: r.arrival):
+    for r in sorted(in_prompt, key=lambda r: r.arrival):
+      if r.status is not Status.RUNNING:
+        continue  # preempted above
       if budget == 0:
         break
       n = largest_fitting(r.slot, min(r.remaining, budget))
