@@ -64,7 +64,7 @@ class StepContext:
 
 def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int],
               group_tables: Sequence[np.ndarray], page_size: int, ops: Any,
-              device: torch.device | str) -> StepContext:
+              device: torch.device | str, token_arrays: Sequence[np.ndarray] | None = None) -> StepContext:
   """Builds the step's metadata on the host and moves it to the device in one copy.
 
   lengths_before[i]: tokens already cached for entry i.  group_tables[g]: the
@@ -79,7 +79,9 @@ def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int],
   np.cumsum(q_lens, out=cu_q[1:])
   num_tokens = int(cu_q[-1])
   q_start = np.asarray(lengths_before, dtype=np.int32)
-  token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+  if token_arrays is None:  # (the caller may have made arrays of the tokens already)
+    token_arrays = [np.asarray(e.tokens) for e in entries]
+  token_ids = np.concatenate(token_arrays).astype(np.int32, copy=False)
   token_seq = np.repeat(np.arange(num_seqs, dtype=np.int32), q_lens)
   positions = (np.arange(num_tokens, dtype=np.int32) - cu_q[:-1][token_seq] + q_start[token_seq])
   slots = np.array([e.slot for e in entries], dtype=np.int32)

@@ -139,15 +139,15 @@ class Engine:
 
   def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
     vocab = self.model.spec.vocab_size
-    for e in entries:
-      ids = np.asarray(e.tokens)
+    token_arrays = [np.asarray(e.tokens) for e in entries]
+    for ids in token_arrays:
       if ids.size and (ids.min() < 0 or ids.max() >= vocab):
         bad = ids[(ids < 0) | (ids >= vocab)][0]
         raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
     lengths = [self.cache.length(e.slot) for e in entries]
     self.cache.extend([(e.slot, len(e.tokens)) for e in entries])
     ctx = pack_step(entries, lengths, [g.tables for g in self.cache.groups],
-                    self.cache.page_size, self.ops, self.device)
+                    self.cache.page_size, self.ops, self.device, token_arrays)
     ctx.older_keys_settled = True  # what the cache holds below a request's length comes from earlier steps
     return ctx
 
