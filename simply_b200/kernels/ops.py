@@ -54,7 +54,9 @@ def _code(t: torch.Tensor) -> int:
 
 
 def _ptr(t: torch.Tensor | None):
-  return None if t is None else ctypes.c_void_p(t.data_ptr())
+  """The tensor's address as the plain integer that a declared `c_void_p` parameter takes (every
+  entry point's parameter types are declared; None is the null pointer)."""
+  return None if t is None else t.data_ptr()
 
 
 class KernelError(RuntimeError):
