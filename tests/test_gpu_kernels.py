@@ -260,11 +260,20 @@ def test_linear_tcgen05(table, tile_n, m, n, k):
 @pytest.mark.parametrize("m", [1, 8, 13, 40])
 @pytest.mark.parametrize("f,k,act", [(160, 96, 0), (1000, 64, 1), (9216 // 4, 2304, 0)])
 def test_gated_linear(table, m, f, k, act):
+  torch.manual_seed(1000 * m + f)
   for dtype in DTYPES:
     ops, ref = table[dtype], ReferenceOps(dtype)
     x = torch.randn(m, k).to(dtype)
     w = (torch.randn(2 * f, k) / k ** 0.5 * 2).to(dtype)
-    close(ops.gated_linear(x.cuda(), w.cuda(), act), ref.gated_linear(x, w, act), dtype, 2.0)
+    got, want = ops.gated_linear(x.cuda(), w.cuda(), act), ref.gated_linear(x, w, act)
+    if dtype == torch.float32:
+      close(got, want, dtype, 2.0)
+    else:
+      # Three bfloat16 roundings stand between the float32 sums and the result (gate, up, their
+      # product), and two right implementations may land one unit in the last place (2^-8) apart
+      # at each: 1.17 % at most, where the common bound for one rounding is 1 %.  (With unseeded
+      # inputs this test met such an element about once in twenty runs.)
+      torch.testing.assert_close(got.float().cpu(), want.float().cpu(), atol=2e-2, rtol=3.2 * 2.0 ** -8)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
