@@ -30,3 +30,18 @@ def test_reference_arm_prints_one_json_line():
   line = json.loads(lines[0])
   assert line["impl"] == "reference"
   assert "unavailable" in line or "value" in line
+
+
+def test_measured_peaks_are_found_flat_or_nested(tmp_path, monkeypatch):
+  sys.path.insert(0, ROOT)
+  import bench
+
+  assert bench._find_number({"hbm_gbs": 6700.5}, "hbm_gbs") == 6700.5
+  assert bench._find_number({"peaks": {"bf16_tflops": {"value": 1600, "clock_mhz": 1900}}}, "bf16_tflops") == 1600.0
+  assert bench._find_number({"runs": [{"x": 1}, {"hbm_gbs": 6600}]}, "hbm_gbs") == 6600.0
+  assert bench._find_number({"hbm_gbs": "n/a"}, "hbm_gbs") is None
+  monkeypatch.setattr(bench, "ROOT", str(tmp_path))
+  assert bench.load_peaks() == (bench.FALLBACK_PEAKS, "fallback")
+  (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps({"hbm_gbs": 6800, "bf16_tflops": 1500}))
+  peaks, where = bench.load_peaks()
+  assert where == "measured" and peaks["hbm_gbs"] == 6800.0 and peaks["bf16_tflops_sustained"] == 1500.0
