@@ -2,9 +2,9 @@
 
 Requests live in *slots*.  Caches with a growing need (keys and values) are
 kept in pages.  Caches whose need for pages is the same (all tokens, or a
-window of W tokens) form a *group*: a group has one pool of page ids and one
-block table per slot, and a page id is valid in the storage of every cache of
-its group.  Caches of fixed size per request (`SlotStateNeed`) are rows of a
+window of W tokens) form a *group*: a group has one pool of page ids, sized
+for what its caches can hold at once, and one block table per slot, and a
+page id is valid in the storage of every cache of its group.  Caches of fixed size per request (`SlotStateNeed`) are rows of a
 tensor indexed by slot.
 
 Bookkeeping follows the reference's `DecodeState`
@@ -44,12 +44,17 @@ def _cdiv(a: int, b: int) -> int:
 
 
 class PageGroup:
-  """Pages and block tables of the caches that share one window."""
+  """Pages and block tables of the caches that share page ids (equal `need.group_key()`).
 
-  def __init__(self, window: int | None, page_size: int, num_pages: int, max_slots: int,
+  The group's pool has a size of its own, and which pages a request may give back is the
+  need's rule (`need.first_needed_page`), not the group's."""
+
+  def __init__(self, need: PagedKVNeed, page_size: int, num_pages: int, max_slots: int,
                max_seq_len: int):
-    self.window = window
+    self.need = need
+    self.window = getattr(need, "window", None)
     self.page_size = page_size
+    self.num_pages = num_pages
     self.pool = PagePool(num_pages)
     self.max_pages_per_seq = _cdiv(max_seq_len, page_size)
     self.tables = np.full((max_slots, self.max_pages_per_seq), -1, dtype=np.int32)
@@ -62,10 +67,8 @@ class PageGroup:
   def plan(self, slot: int, cur_len: int, n_new: int) -> tuple[int, int]:
     """(pages to give back, pages to take) for `n_new` tokens after `cur_len` cached ones."""
     first, end = int(self.first_page[slot]), int(self.end_page[slot])
-    new_first = first
-    if self.window is not None:
-      new_first = max(first, max(cur_len - (self.window - 1), 0) // self.page_size)
-      new_first = min(new_first, end)
+    new_first = max(first, int(self.need.first_needed_page(np.array([cur_len]), self.page_size)[0]))
+    new_first = min(new_first, end)
     new_end = max(end, _cdiv(cur_len + n_new, self.page_size))
     return new_first - first, new_end - end
 
@@ -133,8 +136,19 @@ class CacheManager:
       dtype: torch.dtype = torch.float32,
       device: torch.device | str | None = "cpu",
       poison_freed_pages: bool = False,
+      step_tokens: int | None = None,
+      burst_tokens: int = 1,
+      windowed_cache_tokens: int = 0,
   ):
-    """`device=None` keeps the books only (no storage), for host-side tests."""
+    """`device=None` keeps the books only (no storage), for host-side tests.
+
+    `max_cache_tokens` sizes the pool of a group that keeps every token.  A group that gives
+    pages back asks its need how many pages it can ever hold at once (`need.pool_pages`, from
+    `step_tokens` prompt tokens per step over all requests and `burst_tokens` decoded tokens per
+    request between two looks at the tables) and gets that many, never more than the former;
+    `step_tokens=None` gives every group the full size, `windowed_cache_tokens > 0` fixes the
+    size of those groups (the reference's `global_total_num_pages` and `local_total_num_pages`,
+    simply/serving/page_server.py:175-196)."""
     self.page_size = page_size
     self.max_slots = max_slots
     self.max_seq_len = max_seq_len
@@ -143,24 +157,31 @@ class CacheManager:
     self.groups: list[PageGroup] = []
     self.paged: dict[str, PagedCache] = {}
     self.states: dict[str, SlotState] = {}
-    group_of_window: dict[int | None, int] = {}
+    group_of_key: dict[tuple, int] = {}
     for name, need in needs.items():
       if need is None:
         continue
       if isinstance(need, PagedKVNeed):
-        if need.window is not None and need.window <= 0:
-          raise ValueError(f"cache {name!r}: window must be positive, got {need.window}")
-        g = group_of_window.get(need.window)
+        window = getattr(need, "window", None)
+        if window is not None and window <= 0:
+          raise ValueError(f"cache {name!r}: window must be positive, got {window}")
+        g = group_of_key.get(need.group_key())
         if g is None:
           g = len(self.groups)
-          group_of_window[need.window] = g
-          self.groups.append(
-              PageGroup(need.window, page_size, self.num_pages, max_slots, max_seq_len))
+          group_of_key[need.group_key()] = g
+          pages = self.num_pages
+          if step_tokens is not None:
+            pages = need.pool_pages(page_size=page_size, max_slots=max_slots, max_seq_len=max_seq_len,
+                                    all_pages=self.num_pages, step_tokens=step_tokens,
+                                    burst_tokens=burst_tokens)
+            if windowed_cache_tokens > 0 and window is not None:
+              pages = min(self.num_pages, _cdiv(windowed_cache_tokens, page_size))
+          self.groups.append(PageGroup(need, page_size, max(pages, 1), max_slots, max_seq_len))
         self.groups[g].cache_names.append(name)
         storage = None
         if device is not None:
           storage = torch.zeros(
-              (self.num_pages, 2, need.num_kv_heads, page_size, need.head_dim),
+              (self.groups[g].num_pages, 2, need.num_kv_heads, page_size, need.head_dim),
               dtype=dtype, device=device)
         self.paged[name] = PagedCache(name, g, need, storage)
       elif isinstance(need, SlotStateNeed):
@@ -216,10 +237,9 @@ class CacheManager:
     for g in self.groups:
       if np.any(-(-(cur + new) // self.page_size) > g.end_page[slots]):
         return False
-      if g.window is not None:
-        first = np.minimum(np.maximum(cur - (g.window - 1), 0) // self.page_size, g.end_page[slots])
-        if np.any(first > g.first_page[slots]):
-          return False
+      first = np.minimum(g.need.first_needed_page(cur, self.page_size), g.end_page[slots])
+      if np.any(first > g.first_page[slots]):
+        return False
     return True
 
   def pages_short(self, entries: Sequence[tuple[int, int]]) -> int:
@@ -250,6 +270,10 @@ class CacheManager:
 
   def min_free_pages(self) -> int:
     return min((g.pool.num_free for g in self.groups), default=1 << 30)
+
+  def all_pages_free(self) -> bool:
+    """True when no request holds a page in any group."""
+    return all(g.pool.num_free == g.pool.num_pages for g in self.groups)
 
   def extend(self, entries: Sequence[tuple[int, int]]) -> None:
     """Makes room for the step's new tokens; all or nothing."""
@@ -314,13 +338,11 @@ class CacheManager:
           if int(g.end_page[slot]) != _cdiv(length, self.page_size):
             raise AssertionError(
                 f"slot {slot}: {int(g.end_page[slot])} pages end for {length} tokens")
-          if g.window is None and g.first_page[slot] != 0:
-            raise AssertionError(f"slot {slot}: a group without window gave pages back")
-          if g.window is not None and length > 0:
+          if length > 0:
             # Everything the last cached token can see must still be held.
-            oldest_visible = max(length - g.window, 0)
-            if int(g.first_page[slot]) > oldest_visible // self.page_size:
-              raise AssertionError(f"slot {slot}: pages inside the window were given back")
+            needed = int(g.need.first_needed_page(np.array([length - 1]), self.page_size)[0])
+            if int(g.first_page[slot]) > needed:
+              raise AssertionError(f"slot {slot}: pages that are still visible were given back")
         held.extend(pages)
       free = g.pool.free_pages()
       if len(set(held)) != len(held):

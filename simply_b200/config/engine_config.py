@@ -24,12 +24,21 @@ class EngineConfig:
   # Longest sequence (prompt + generated) of one request; 0 means the model's
   # max_position_embeddings.
   max_seq_len: int = 0
-  # Tokens the cache pool can hold over all live requests; every layer group
-  # gets ceil(max_cache_tokens / page_size) pages.  0 means batch_size * max_seq_len.
+  # Tokens the cache pool can hold over all live requests: a group of layers that keeps every
+  # token gets ceil(max_cache_tokens / page_size) pages.  0 means batch_size * max_seq_len.
   max_cache_tokens: int = 0
+  # Tokens the pool of a group of sliding-window layers holds.  0 sizes it from the window: what
+  # batch_size requests can hold at once when a step brings at most max_num_issue_tokens prompt
+  # tokens (the reference's local_total_num_pages beside global_total_num_pages,
+  # simply/serving/page_server.py:175-196); -1 makes it as large as max_cache_tokens, for callers
+  # of `step_raw` that bring longer portions than max_num_issue_tokens.
+  max_window_cache_tokens: int = 0
   # Token budget of one step (decoded tokens and prompt portions together);
   # 0 means 2048.
   max_num_issue_tokens: int = 0
+  # In bfloat16, keep matrices that the model folder stores in 32 bits as they are (twice the
+  # memory, products on the 32-bit kernel) instead of narrowing them to the activation dtype.
+  keep_float32_weights: bool = False
   # Replay decode-only steps from CUDA graphs.
   use_cuda_graphs: bool = True
   # Decode steps that run in a row without the host in between (the reference's flag of
@@ -52,6 +61,8 @@ class EngineConfig:
     for k in ("max_seq_len", "max_cache_tokens", "max_num_issue_tokens"):
       if getattr(self, k) < 0:
         raise ValueError(f"{k} must be >= 0, got {getattr(self, k)}")
+    if self.max_window_cache_tokens < -1:
+      raise ValueError(f"max_window_cache_tokens must be >= -1, got {self.max_window_cache_tokens}")
 
   def resolved(self, model_max_context: int) -> "EngineConfig":
     """Fills the zero defaults from the model's longest context."""

@@ -123,6 +123,11 @@ class Gemma2Config:
     d["layer_types"] = list(self.resolved_layer_types())
     if isinstance(d["eos_token_id"], tuple):
       d["eos_token_id"] = list(d["eos_token_id"])
+    # Whole numbers are written as integers, as published config.json files have them (other
+    # readers of such a folder insist on an integer query_pre_attn_scalar).
+    for key in ("query_pre_attn_scalar", "rope_theta"):
+      if float(d[key]).is_integer():
+        d[key] = int(d[key])
     return d
 
   def replace(self, **changes: Any) -> "Gemma2Config":

@@ -682,3 +682,27 @@ extern "C" int sb_decode_advance(const int* sampled, int* token_ids, int* positi
   SB_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Keeps the logits of one decode step of a burst: history[step, :] = logits, with `step` read
+// from the burst's device-side counter (launched before decode_advance moves the counter on).
+// Only used when the decode runner is asked to keep logits, so that tests can compare the rows a
+// CUDA-graph replay produced with a plain model's.
+// ---------------------------------------------------------------------------
+__global__ void keep_logits_kernel(const float* __restrict__ logits, float* __restrict__ history,
+                                   const int* __restrict__ step_counter, size_t n) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const size_t step = (size_t)*step_counter;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) history[step * n + i] = logits[i];
+}
+
+extern "C" int sb_keep_logits(const float* logits, float* history, const int* step_counter, long long n,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  sb_launch(keep_logits_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, logits, history, step_counter,
+            (size_t)n);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

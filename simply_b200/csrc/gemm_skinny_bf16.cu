@@ -1,5 +1,7 @@
 // Weight-streaming matrix product for a handful of tokens (decode steps):
-//   out[M, N] = x[M, K] . w[N, K]^T,  bfloat16 in, float32 accumulate, M <= 32.
+//   out[M, N] = x[M, K] . w[N, K]^T,  bfloat16 in, float32 accumulate, M <= 32
+// (the kernel table sends the products of steps of up to 16 tokens here, and the output layer's
+// rows in chunks of up to 32).
 //
 // With so few rows the product is bound by reading w once from HBM, so the kernel
 // is built around that stream.  The weight matrix is the 16-row operand of

@@ -11,8 +11,14 @@ simply/utils/ragged_paged_attention.py:2064-2102, simply/serving/common_flags.py
 without a tracing compiler.
 
 The pages for all n tokens of every request are taken before the burst, so block
-tables do not change inside it.  The split-key attention work lists cover the keys
-of the whole burst; chunks with nothing visible at a given step come out empty.
+tables do not change inside it.  What a mixer prepares on the host per step (the
+split-key attention work lists) it hands over as plans (`Mixer.graph_plans`): the
+runner gives each plan a piece of the static buffer and lets it refill that piece
+before a burst; the lists cover the keys of the whole burst, and chunks with nothing
+visible at a given step come out empty.
+
+Which models run this way is the parts' own statement (`graph_safe`), not a list kept
+here: any registered part that keeps to device tensors and `ctx.memo` takes part.
 """
 
 from __future__ import annotations
@@ -27,21 +33,13 @@ import torch
 
 from simply_b200.engine.batch import StepContext
 from simply_b200.kernels.ops import KernelError
-from simply_b200.parts.attention import PagedAttention
 
 
 def graphable(model: Any) -> bool:
-  """Graphs are used when every layer is made of the package's own parts: a foreign mixer,
-  feed-forward, block or position encoding may read host-side metadata that a replay does not
-  refresh, or synchronise with the host, which a capture forbids."""
-  from simply_b200.parts.block import PreNormBlock, SandwichNormBlock
-  from simply_b200.parts.feedforward import GatedFeedForward
-  from simply_b200.parts.position import NoPositionEncoding, RotaryEncoding
-
-  return all(
-      type(b) in (SandwichNormBlock, PreNormBlock) and type(b.mixer) is PagedAttention
-      and type(b.mixer.position) in (RotaryEncoding, NoPositionEncoding)
-      and type(b.feed_forward) is GatedFeedForward for b in model.blocks.values())
+  """Graphs are used when every part says that its step may be captured (`Part.graph_safe`):
+  a part that reads host-side metadata, which a replay does not refresh, or waits for the
+  device, which a capture forbids, leaves the flag at its default and the model runs eagerly."""
+  return bool(model.graph_safe())
 
 
 @dataclasses.dataclass
@@ -58,8 +56,8 @@ class _Graph:
   captured: bool
   batch: int
   bucket: int
-  chunks: dict
   launches: int
+  logits_history: torch.Tensor | None = None  # [MAX_BURST, batch, vocab] when logits are kept
   resume: dict | None = None  # what the device holds after the last burst (see DecodeRunner.run)
   graph_exec: Any = None  # the instantiated graph's handle and the buffers' addresses, for the native launch
   pointers: tuple = ()
@@ -73,13 +71,11 @@ class DecodeRunner:
     self.engine = engine
     self.ops = engine.ops
     self.graphs: dict[tuple[int, int], _Graph] = {}
-    # Kinds of attention by (window, group), each with the kv heads and head size of its first layer.
-    kinds: dict[tuple, tuple[int, int]] = {}
-    for b in engine.model.blocks.values():
-      kinds.setdefault((b.mixer.window, b.mixer.num_heads // b.mixer.num_kv_heads),
-                       (b.mixer.num_kv_heads, b.mixer.head_dim))
-    self.attn_kinds = sorted(kinds, key=lambda k: (k[0] or 0, k[1]))
-    self.attn_shapes = kinds
+    # True keeps the float32 logits of every step of a burst on the device (`last_logits` after
+    # `run`): tests compare the rows a replay produced with a plain model's.  Set before the
+    # first burst; costs MAX_BURST * batch * vocab floats per graph.
+    self.keep_logits = False
+    self.last_logits: torch.Tensor | None = None
     self.stream = torch.cuda.Stream(device=engine.device)
     self._stream_ptr = ctypes.c_void_p(self.stream.cuda_stream)
     self.pool = torch.cuda.graph_pool_handle()
@@ -102,11 +98,15 @@ class DecodeRunner:
     return max(live, min(size, self.engine.cache.max_slots))
 
   # ---- layout of the static buffer -----------------------------------------------
-  def _span(self, bucket: int, window: int | None) -> int:
-    """Most keys a sequence of this bucket sees in a layer with this window during a burst."""
-    return min(bucket, window + self.MAX_BURST + 64) if window else bucket
+  def _plans(self, batch: int, bucket: int) -> list:
+    """The plans of all mixers for this graph, one per memo key (layers of one kind share theirs)."""
+    plans: dict[Any, Any] = {}
+    for block in self.engine.model.blocks.values():
+      for plan in block.mixer.graph_plans(self.ops, batch, bucket, self.MAX_BURST, self.engine.cache.page_size):
+        plans.setdefault(plan.key, plan)
+    return list(plans.values())
 
-  def _layout(self, batch: int, bucket: int, chunks: dict) -> tuple[dict, dict, int]:
+  def _layout(self, batch: int, bucket: int, plans: list) -> tuple[dict, int]:
     cache = self.engine.cache
     views, off = {}, 0
 
@@ -122,24 +122,15 @@ class DecodeRunner:
     take("sample_params", batch * 6)
     for gi, g in enumerate(cache.groups):
       take(f"table{gi}", batch * g.max_pages_per_seq)
-    items_per_seq = {}
-    for window, group in self.attn_kinds:
-      per_seq = -(-self._span(bucket, window) // chunks[(window, group)]) + 1
-      items_per_seq[(window, group)] = per_seq
-      take(f"items{window}_{group}", batch * per_seq * 2)
-      take(f"split_start{window}_{group}", batch)
-      take(f"split_count{window}_{group}", batch)
-    return views, items_per_seq, off
+    for i, plan in enumerate(plans):
+      take(f"plan{i}", plan.words)
+    return views, off
 
   def _prepare(self, batch: int, bucket: int) -> _Graph:
     """Static buffers and the step closure for one (batch, bucket); nothing runs yet."""
     eng, ops = self.engine, self.ops
-    chunks = {}
-    for window, group in self.attn_kinds:
-      span = self._span(bucket, window)
-      chunks[(window, group)] = ops.decode_chunk_for([bucket - span] * batch, [bucket] * batch,
-                                                     *self.attn_shapes[(window, group)])
-    views, items_per_seq, words = self._layout(batch, bucket, chunks)
+    plan_list = self._plans(batch, bucket)
+    views, words = self._layout(batch, bucket, plan_list)
     meta = torch.zeros(words, dtype=torch.int32, device=eng.device)
     host = torch.zeros(words, dtype=torch.int32).pin_memory()
 
@@ -154,26 +145,27 @@ class DecodeRunner:
         token_seq=view("token_seq"), cu_q=view("cu_q"), q_start=view("q_start"), slots=view("slots"),
         block_tables=block_tables, logit_rows=view("logit_rows"), max_q_len=1, max_kv_len=bucket,
         page_size=eng.cache.page_size, older_keys_settled=True)
-    plans = {}
-    for (window, group), per_seq in items_per_seq.items():
-      plans[(window, group)] = dict(
-          num_prefill=0, num_decode=batch * per_seq, chunk=chunks[(window, group)], rows_max=group,
-          rows_per_tile=64,
-          prefill_items=None, decode_items=view(f"items{window}_{group}"),
-          split_start=view(f"split_start{window}_{group}"), split_count=view(f"split_count{window}_{group}"))
+    bound = {plan.key: plan.bind(view(f"plan{i}")) for i, plan in enumerate(plan_list)}
+    plans = {f"plan{i}": plan for i, plan in enumerate(plan_list)}
     sampled = torch.zeros(batch, dtype=torch.int32, device=eng.device)
     history = torch.zeros(self.MAX_BURST, batch, dtype=torch.int32, device=eng.device)
     host_history = torch.zeros(self.MAX_BURST, batch, dtype=torch.int32).pin_memory()
+    logits_history = None
+    if self.keep_logits:
+      logits_history = torch.zeros(self.MAX_BURST, batch, eng.model.spec.vocab_size, dtype=torch.float32,
+                                   device=eng.device)
 
     def one_step():
-      ctx.memo = {("attention_plan", w, gr): p for (w, gr), p in plans.items()}
+      ctx.memo = dict(bound)
       logits = eng.model.forward(ctx, eng.caches)
+      if logits_history is not None:
+        ops.keep_logits(logits, logits_history, view("step_counter"))
       ops.sample_device(logits, view("sample_params").view(batch, 6), sampled)
       ops.decode_advance(sampled, view("token_ids"), view("positions"), view("q_start"),
                          view("sample_params"), history, view("step_counter"))
 
     g = _Graph(torch.cuda.CUDAGraph(), meta, host, views, plans, sampled, history, host_history, one_step,
-               False, batch, bucket, chunks, 0)
+               False, batch, bucket, 0, logits_history)
     self._fill_constants(g)
     return g
 
@@ -221,12 +213,11 @@ class DecodeRunner:
 
   # ---- running -----------------------------------------------------------------------
   def _chunk_ranges(self, g, lengths: np.ndarray, steps: int) -> list:
-    return [self.ops.decode_chunk_range(lengths, steps, window, plan["chunk"])
-            for (window, _), plan in g.plans.items()]
+    return [plan.ranges(lengths, steps) for plan in g.plans.values()]
 
   @staticmethod
   def _same_ranges(a: list, b: list) -> bool:
-    return all(np.array_equal(x[0], y[0]) and np.array_equal(x[1], y[1]) for x, y in zip(a, b))
+    return all(len(x) == len(y) and all(np.array_equal(p, q) for p, q in zip(x, y)) for x, y in zip(a, b))
 
   def run(self, slots: Sequence[int], last_tokens: Sequence[int], sample_params: np.ndarray,
           steps: int) -> np.ndarray:
@@ -296,12 +287,9 @@ class DecodeRunner:
       put("sample_params", sample_params)
       for gi, grp in enumerate(cache.groups):
         put(f"table{gi}", grp.tables[np.asarray(slots)])
-      for (window, group), plan in g.plans.items():
-        per_seq = plan["num_decode"] // batch
-        items, start, count = self.ops.static_decode_plan(lengths, steps, window, plan["chunk"], per_seq)
-        put(f"items{window}_{group}", items)
-        put(f"split_start{window}_{group}", start)
-        put(f"split_count{window}_{group}", count)
+      for name, plan in g.plans.items():
+        o, n = g.views[name]
+        plan.fill(h[o:o + n], lengths, steps)
     # Copy, replays and read-back run on the runner's own stream, the one the graph was captured
     # on, issued by one native call.  (A burst that goes on from the last one needs no order with
     # the engine's stream: nothing ran there for these requests since, or their lengths would differ.)
@@ -342,6 +330,8 @@ class DecodeRunner:
     if rc != 0:
       raise KernelError(f"decode burst: CUDA error {rc}")
     out = g.host_history[rows].numpy()[:, :live].copy()
+    if g.logits_history is not None:
+      self.last_logits = g.logits_history[rows, :live].clone()
     self.ops.launches += g.launches * replays
     eng.num_steps += steps
     return out

@@ -48,6 +48,14 @@ class GenerationResult:
     return self.finish_reason != "eos"
 
 
+def _derived_seed(n: int) -> int:
+  """The n-th of a fixed sequence of well-mixed 64-bit seeds (splitmix64)."""
+  z = (0x9E3779B97F4A7C15 * (n + 1)) & 0xFFFFFFFFFFFFFFFF
+  z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+  z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+  return z ^ (z >> 31)
+
+
 def default_ops(dtype: torch.dtype):
   """The CUDA kernel table; fails loudly when there is no GPU or the extension cannot be built."""
   from simply_b200.kernels.ops import CudaOps
@@ -73,13 +81,17 @@ class Engine:
     self.cache = CacheManager(
         self.model.cache_needs(), page_size=ec.page_size, max_slots=ec.batch_size,
         max_seq_len=ec.max_seq_len, max_cache_tokens=ec.max_cache_tokens, dtype=self.dtype,
-        device=self.device, poison_freed_pages=ec.poison_freed_pages)
+        device=self.device, poison_freed_pages=ec.poison_freed_pages,
+        step_tokens=None if ec.max_window_cache_tokens < 0 else ec.max_num_issue_tokens,
+        burst_tokens=min(max(ec.intermediate_steps, 1), 64),
+        windowed_cache_tokens=max(ec.max_window_cache_tokens, 0))
     self.caches = {**self.cache.paged, **self.cache.states}
     eos = getattr(config, "eos_token_id", None)
     eos_ids = () if eos is None else (tuple(eos) if isinstance(eos, (tuple, list)) else (eos,))
     self.scheduler = Scheduler(self.cache, max_num_issue_tokens=ec.max_num_issue_tokens,
                                max_seq_len=ec.max_seq_len, eos_ids=eos_ids)
     self._next_id = 0
+    self._unseeded = 0  # requests that came without a sampling seed so far
     self.num_steps = 0
     self._decode_runner = None
     if ec.use_cuda_graphs and self.device.type == "cuda" and hasattr(self.ops, "decode_advance"):
@@ -99,7 +111,8 @@ class Engine:
       device = "cuda" if ops is None else "cpu"
     if ops is None:
       ops = default_ops(dtype)
-    tensors = load_tensors(model_dir, DecoderModel(config.model_spec()).tensor_specs(), dtype, device)
+    tensors = load_tensors(model_dir, DecoderModel(config.model_spec()).tensor_specs(), dtype, device,
+                           keep_float32=ec.keep_float32_weights)
     return cls(config, tensors, ec, ops=ops, device=device)
 
   @classmethod
@@ -125,8 +138,16 @@ class Engine:
   def close_request(self, slot: int) -> None:
     self.cache.release_slot(slot)
 
-  def step_raw(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
-    """Runs one batch; returns float32 logits [wanted, vocab] (None if nothing is wanted)."""
+  def step_raw(self, entries: Sequence[StepEntry], *, from_graph: bool = False) -> torch.Tensor | None:
+    """Runs one batch; returns float32 logits [wanted, vocab] (None if nothing is wanted).
+
+    `from_graph=True` lets a step in which every entry brings one token run the way generation
+    runs such steps, as a replay of the decode graph (when the engine has graphs at all and keeps
+    their logits); the tokens the graph samples on the way are dropped."""
+    runner = self._decode_runner
+    if (from_graph and runner is not None and runner.keep_logits
+        and all(len(e.tokens) == 1 for e in entries)):
+      return self._step_raw_from_graph(entries)
     ctx = self._prepare(entries)
     hold = getattr(self.ops, "hold_stream", None)  # (a kernel table without streams has none)
     if hold is None:
@@ -137,13 +158,30 @@ class Engine:
     self.num_steps += 1
     return logits
 
-  def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+  def _step_raw_from_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+    self._check_token_ids([np.asarray(e.tokens) for e in entries])
+    for i, e in enumerate(entries):
+      if any(w != 0 for w in e.want):
+        raise ValueError(f"entry {i}: wanted place outside its 1 token")
+    lengths = [self.cache.length(e.slot) + 1 for e in entries]
+    params = self.ops.pack_sample_params([0.0] * len(entries), [-1] * len(entries), [1.0] * len(entries),
+                                         [0] * len(entries), lengths)
+    self._decode_runner.run([e.slot for e in entries], [int(e.tokens[0]) for e in entries], params, 1)
+    rows = [i for i, e in enumerate(entries) if len(e.want)]
+    if not rows:
+      return None
+    return self._decode_runner.last_logits[0][rows]
+
+  def _check_token_ids(self, token_arrays) -> None:
     vocab = self.model.spec.vocab_size
-    token_arrays = [np.asarray(e.tokens) for e in entries]
     for ids in token_arrays:
       if ids.size and (ids.min() < 0 or ids.max() >= vocab):
         bad = ids[(ids < 0) | (ids >= vocab)][0]
         raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
+
+  def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    token_arrays = [np.asarray(e.tokens) for e in entries]
+    self._check_token_ids(token_arrays)
     lengths = [self.cache.length(e.slot) for e in entries]
     self.cache.extend([(e.slot, len(e.tokens)) for e in entries])
     ctx = pack_step(entries, lengths, [g.tables for g in self.cache.groups],
@@ -157,7 +195,13 @@ class Engine:
     if request_id is None:
       request_id = self._next_id
       self._next_id += 1
-    return self.scheduler.add(request_id, prompt, params or SamplingParams())
+    params = params or SamplingParams()
+    if params.seed is None:
+      # No seed given: one per request, from the order of arrival, so that equal prompts draw
+      # different samples (a run of the same requests in the same order still repeats itself).
+      params = dataclasses.replace(params, seed=_derived_seed(self._unseeded))
+      self._unseeded += 1
+    return self.scheduler.add(request_id, prompt, params)
 
   def cancel(self, request_id: object) -> bool:
     return self.scheduler.cancel(request_id)

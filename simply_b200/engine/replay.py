@@ -30,10 +30,8 @@ from simply_b200.config import EngineConfig
 from simply_b200.engine.batch import StepEntry
 from simply_b200.engine.engine import Engine
 
-MAX_LIVE_REQUESTS = 4
-
-
-def replay(engine: Engine, lines: IO[str], out_dir: str, out: IO[str] = sys.stdout) -> int:
+def replay(engine: Engine, lines: IO[str], out_dir: str, out: IO[str] = sys.stdout,
+           from_graph: bool = False) -> int:
   os.makedirs(out_dir, exist_ok=True)
   slots: dict[object, int] = {}
   steps = 0
@@ -51,7 +49,7 @@ def replay(engine: Engine, lines: IO[str], out_dir: str, out: IO[str] = sys.stdo
       entries.append(StepEntry(slots[rid], [int(t) for t in e["tokens"]],
                                [int(w) for w in e.get("want", [])]))
     if entries:
-      logits = engine.step_raw(entries)
+      logits = engine.step_raw(entries, from_graph=from_graph)
       if logits is not None:
         arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
         arr.tofile(os.path.join(out_dir, f"{step}.f32"))
@@ -65,17 +63,24 @@ def replay(engine: Engine, lines: IO[str], out_dir: str, out: IO[str] = sys.stdo
 
 
 def engine_for_replay(model_dir: str, dtype: str, max_tokens: int, page_size: int = 64,
-                      poison_freed_pages: bool = False, ops=None) -> Engine:
-  """An engine whose cache pool holds `max_tokens` tokens (rounded up to whole pages)."""
+                      poison_freed_pages: bool = False, ops=None, max_live: int = 4,
+                      cuda_graphs: bool = False) -> Engine:
+  """An engine whose cache pool holds `max_tokens` tokens (rounded up to whole pages) and that
+  serves up to `max_live` requests at a time.  With `cuda_graphs`, steps in which every request
+  brings one token are replayed from the decode graphs that generation uses."""
   from simply_b200.config import load_config
 
   max_context = load_config(model_dir).model_spec().max_context
   pages = -(-max_tokens // page_size)
   ec = EngineConfig(
-      activation_dtype=dtype, page_size=page_size, batch_size=MAX_LIVE_REQUESTS,
+      activation_dtype=dtype, page_size=page_size, batch_size=max_live,
       max_seq_len=max_context, max_cache_tokens=pages * page_size,
-      poison_freed_pages=poison_freed_pages, use_cuda_graphs=False)
-  return Engine.from_folder(model_dir, ec, ops=ops)
+      max_window_cache_tokens=-1,  # a trace may bring a portion of any length in one step
+      poison_freed_pages=poison_freed_pages, use_cuda_graphs=cuda_graphs)
+  engine = Engine.from_folder(model_dir, ec, ops=ops)
+  if engine._decode_runner is not None:
+    engine._decode_runner.keep_logits = True
+  return engine
 
 
 def main(argv=None) -> int:
@@ -90,8 +95,11 @@ def main(argv=None) -> int:
   ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page (default 64)")
   ap.add_argument("--poison-freed-pages", action="store_true",
                   help="fill pages that are given back with NaN (shows reads of pages not held)")
+  ap.add_argument("--max-live", type=int, default=4, help="requests that may be live at a time (default 4)")
+  ap.add_argument("--cuda-graphs", action="store_true",
+                  help="replay steps that bring one token per request from the decode graphs of generation")
   args = ap.parse_args(argv)
   engine = engine_for_replay(args.model, args.dtype, args.max_tokens, args.page_size,
-                             args.poison_freed_pages)
-  replay(engine, sys.stdin, args.out)
+                             args.poison_freed_pages, max_live=args.max_live, cuda_graphs=args.cuda_graphs)
+  replay(engine, sys.stdin, args.out, from_graph=args.cuda_graphs)
   return 0

@@ -6,7 +6,7 @@ CPU path.  `dtype` is the activation and cache dtype: `torch.bfloat16` is the
 serving path, `torch.float32` runs the whole model in true 32-bit arithmetic on
 CUDA cores (own SIMT matrix product, no tensor-core mode).
 
-Matrix products: in bfloat16, steps with at most 32 tokens use the engine's own
+Matrix products: in bfloat16, steps with at most 16 tokens use the engine's own
 weight-streaming kernel (with fused soft-cap or gated-activation epilogues);
 larger ones go to the library product (cuBLAS through torch.mm), as the
 reference leaves them to XLA.  Everything else (attention over the paged cache,
@@ -74,6 +74,42 @@ class _HeldStream:
 
   def __exit__(self, *exc):
     self.ops._step_stream = self.previous
+
+
+class AttentionGraphPlan:
+  """Static work list of the split-key attention kernel for decode bursts replayed from a CUDA
+  graph, for one kind of attention layer (see `Mixer.graph_plans` for the interface).
+
+  Every sequence gets the same number of work items, so the launch has a fixed size: the chunks
+  that hold keys between the lowest key visible at the burst's first step and the highest at its
+  last, then fillers.  The words are: items [batch * per_seq, 2], split_start [batch],
+  split_count [batch]."""
+
+  def __init__(self, ops: "CudaOps", window: int | None, group: int, num_kv_heads: int, head_dim: int,
+               batch: int, bucket: int, max_burst: int, page_size: int):
+    self.key = ops._plan_key(window, group, num_kv_heads, head_dim, page_size)
+    self.window, self.group, self.batch = window, group, batch
+    # Most keys a sequence of this bucket sees in such a layer during a burst.
+    span = min(bucket, window + max_burst + 64) if window else bucket
+    self.chunk = ops.decode_chunk_for([bucket - span] * batch, [bucket] * batch, num_kv_heads, head_dim)
+    self.per_seq = -(-span // self.chunk) + 1
+    self.words = batch * self.per_seq * 2 + 2 * batch
+
+  def bind(self, view: torch.Tensor) -> dict:
+    n = self.batch * self.per_seq * 2
+    return dict(num_prefill=0, num_decode=self.batch * self.per_seq, chunk=self.chunk, rows_max=self.group,
+                rows_per_tile=64, prefill_items=None, decode_items=view[:n],
+                split_start=view[n:n + self.batch], split_count=view[n + self.batch:])
+
+  def fill(self, host_words: np.ndarray, lengths: np.ndarray, steps: int) -> None:
+    items, start, count = CudaOps.static_decode_plan(lengths, steps, self.window, self.chunk, self.per_seq)
+    n = items.size
+    host_words[:n] = items.reshape(-1)
+    host_words[n:n + self.batch] = start
+    host_words[n + self.batch:] = count
+
+  def ranges(self, lengths: np.ndarray, steps: int):
+    return CudaOps.decode_chunk_range(lengths, steps, self.window, self.chunk)
 
 
 class CudaOps:
@@ -149,6 +185,7 @@ class CudaOps:
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_gemm_tcgen05": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
+        "sb_keep_logits": [c_void, c_void, c_void, c_ll, c_void],
     }
     for name, argtypes in protos.items():
       fn = getattr(self.lib, name)
@@ -332,16 +369,36 @@ class CudaOps:
       self._tensor_maps[key] = buf
     return ctypes.c_void_p(buf[1]) if buf[1] is not None else None
 
+  def _prefill_uses_tcgen05(self, head_dim: int, group: int, page_size: int) -> bool:
+    return (self.prefill_tcgen05 and head_dim % 64 == 0 and 128 % group == 0
+            and page_size & (page_size - 1) == 0)
+
+  def _plan_key(self, window: int | None, group: int, num_kv_heads: int, head_dim: int, page_size: int) -> tuple:
+    """Where a step keeps the work lists of one kind of attention layer in `ctx.memo`.  Layers
+    share lists only if everything the lists are cut for agrees: the window, the group, the
+    number of kv heads and the head size (they set the chunk length) and the rows of a prefill tile."""
+    rows = 128 if self._prefill_uses_tcgen05(head_dim, group, page_size) else (self.prefill_rows or 64)
+    return ("attention_plan", window, group, num_kv_heads, head_dim, rows)
+
+  def attention_graph_plan(self, *, window: int | None, num_heads: int, num_kv_heads: int, head_dim: int,
+                           batch: int, bucket: int, max_burst: int, page_size: int):
+    """The static work list a decode graph needs for one kind of attention layer, or None when
+    the kernel that serves it reads no list (the general kernel)."""
+    group = num_heads // num_kv_heads
+    if not self._uses_tensor_core_attention(head_dim, group):
+      return None
+    return AttentionGraphPlan(self, window, group, num_kv_heads, head_dim, batch, bucket, max_burst, page_size)
+
   def _attention_plan(self, ctx: Any, window: int | None, group: int, force_rows: int = 0,
                       num_kv_heads: int = 1, head_dim: int = 0) -> dict:
-    """Work lists of the two tensor-core kernels for this step, per (window, group).
+    """Work lists of the two tensor-core kernels for this step, per kind of layer (`_plan_key`).
 
     Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
     split-key kernel: their keys are cut into chunks at multiples of `chunk` of the
     absolute position, one work item per chunk.  The others are cut into tiles of
     64 // group or 128 // group tokens for the prefill kernel, heaviest tile first.
     """
-    key = ("attention_plan", window, group)
+    key = self._plan_key(window, group, num_kv_heads, head_dim, ctx.page_size)
     plan = ctx.memo.get(key)
     if plan is not None:
       return plan
@@ -577,8 +634,7 @@ class CudaOps:
     group = num_heads // num_kv_heads
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
       prefill, decode, _, prefill_tc = self._attention_lib(head_dim)
-      use_tc = (self.prefill_tcgen05 and prefill_tc is not None and 128 % group == 0
-                and ctx.page_size & (ctx.page_size - 1) == 0)
+      use_tc = prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
       plan = self._attention_plan(ctx, window, group, 128 if use_tc else 0, num_kv_heads, head_dim)
       common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
                 _ptr(ctx.q_start))
@@ -647,6 +703,10 @@ class CudaOps:
     self._call("sb_sample", _ptr(logits.contiguous()), _ptr(dev_params), _ptr(out), r, vocab, _ptr(scratch))
     self.launches += 2
     return out
+
+  def keep_logits(self, logits: torch.Tensor, history: torch.Tensor, step_counter: torch.Tensor) -> None:
+    """history[step_counter] = logits, without the host knowing the step (tests of graph replays)."""
+    self._call("sb_keep_logits", _ptr(logits), _ptr(history), _ptr(step_counter), logits.numel())
 
   def decode_advance(self, sampled, token_ids, positions, q_start, sample_params, history, step_counter) -> None:
     self._call("sb_decode_advance", _ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(q_start),

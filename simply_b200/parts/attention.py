@@ -53,6 +53,16 @@ class PagedAttention(Mixer):
   def cache_need(self) -> PagedKVNeed:
     return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
 
+  @property
+  def graph_safe(self) -> bool:
+    return self.position.graph_safe
+
+  def graph_plans(self, ops, batch: int, bucket: int, max_burst: int, page_size: int) -> list:
+    plan = ops.attention_graph_plan(
+        window=self.window, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+        batch=batch, bucket=bucket, max_burst=max_burst, page_size=page_size)
+    return [plan] if plan is not None else []
+
   def tensor_specs(self) -> list[TensorSpec]:
     specs = [self.q_proj.spec()]
     if self.project_kv:

@@ -94,6 +94,11 @@ class SandwichNormBlock(Block):
   def cache_need(self):
     return self.mixer.cache_need()
 
+  @property
+  def graph_safe(self) -> bool:
+    return (self.mixer.graph_safe and self.feed_forward.graph_safe
+            and all(n.graph_safe for n in self._norms()))
+
   def tensor_specs(self) -> list[TensorSpec]:
     specs = self.mixer.tensor_specs() + self.feed_forward.tensor_specs()
     for n in self._norms():

@@ -12,11 +12,15 @@ from typing import Any
 
 import torch
 
-from simply_b200.parts.base import Part
-from simply_b200.weights.loader import TensorSpec
+from simply_b200.parts.base import Embedding, Head
+from simply_b200.registry import EMBEDDINGS, HEADS
+from simply_b200.weights.loader import TensorSpec, WeightError
 
 
-class TokenEmbedding(Part):
+@EMBEDDINGS.register("token_embedding")
+class TokenEmbedding(Embedding):
+
+  graph_safe = True
 
   def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0):
     self.name = f"{prefix}.weight"
@@ -36,9 +40,12 @@ class TokenEmbedding(Part):
     return ctx.ops.embed(self.table, ctx.token_ids, self.scale)
 
 
-class TiedHead(Part):
+@HEADS.register("tied_head")
+class TiedHead(Head):
 
-  def __init__(self, prefix: str, embedding: TokenEmbedding, logit_softcap: float = 0.0):
+  graph_safe = True
+
+  def __init__(self, prefix: str, embedding: Embedding, logit_softcap: float = 0.0):
     self.embedding = embedding
     self.logit_softcap = float(logit_softcap or 0.0)
 
@@ -46,6 +53,16 @@ class TiedHead(Part):
     # A folder may repeat the tied table under the output layer's name.
     return [TensorSpec("lm_head.weight", (self.embedding.vocab_size, self.embedding.width),
                        "matrix", optional=True)]
+
+  def bind(self, tensors, ops) -> None:
+    # The tied table may appear a second time under the output layer's name, but only as a copy.
+    duplicate = tensors.get("lm_head.weight")
+    if duplicate is not None:
+      table = tensors[self.embedding.name]
+      if duplicate.shape != table.shape or not torch.equal(duplicate.to(table.dtype), table):
+        raise WeightError([], [], [], [], other=[
+            f"lm_head.weight differs from {self.embedding.name}: this model ties its output layer to "
+            "the embedding table, so the folder may repeat the table but not hold another one"])
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
     return ctx.ops.lm_head(x, self.embedding.table, self.logit_softcap)

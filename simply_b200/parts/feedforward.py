@@ -26,6 +26,8 @@ ACTIVATIONS.register("relu", 2)
 @FEED_FORWARDS.register("gated")
 class GatedFeedForward(FeedForward):
 
+  graph_safe = True
+
   def __init__(self, prefix: str, width: int, hidden: int, activation: str):
     self.prefix = prefix
     self.width = width

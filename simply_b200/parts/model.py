@@ -17,12 +17,12 @@ import torch
 from simply_b200.config.model_spec import ModelSpec
 from simply_b200.parts.base import Block, build_part
 from simply_b200.parts.block import ResidualStream
-from simply_b200.parts.embedding import TiedHead, TokenEmbedding
-from simply_b200.registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from simply_b200.registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
 from simply_b200.weights.loader import TensorSpec
 
 # Importing the part modules registers the built-in parts.
 from simply_b200.parts import attention as _attention  # noqa: F401
+from simply_b200.parts import embedding as _embedding  # noqa: F401
 from simply_b200.parts import feedforward as _feedforward  # noqa: F401
 from simply_b200.parts import norm as _norm  # noqa: F401
 from simply_b200.parts import position as _position  # noqa: F401
@@ -33,9 +33,7 @@ class DecoderModel:
   def __init__(self, spec: ModelSpec):
     spec.validate()
     self.spec = spec
-    if spec.embedding.kind != "token_embedding":
-      raise ValueError(f"unknown embedding kind {spec.embedding.kind!r}")
-    self.embedding = TokenEmbedding(spec.embedding.prefix, **dict(spec.embedding.params))
+    self.embedding = build_part(EMBEDDINGS, spec.embedding)
     self.blocks: dict[str, Block] = {}
     for layer in spec.layers:
       mixer = build_part(MIXERS, layer.mixer)
@@ -43,9 +41,7 @@ class DecoderModel:
       self.blocks[layer.name] = build_part(BLOCKS, layer.block, mixer=mixer,
                                            feed_forward=feed_forward)
     self.final_norm = build_part(NORMS, spec.final_norm)
-    if spec.head.kind != "tied_head":
-      raise ValueError(f"unknown head kind {spec.head.kind!r}")
-    self.head = TiedHead(spec.head.prefix, self.embedding, **dict(spec.head.params))
+    self.head = build_part(HEADS, spec.head, embedding=self.embedding)
     self.cache_names = spec.cache_names()
 
   # ---- weights --------------------------------------------------------------
@@ -66,6 +62,11 @@ class DecoderModel:
       block.bind(tensors, ops)
     self.final_norm.bind(tensors, ops)
     self.head.bind(tensors, ops)
+
+  def graph_safe(self) -> bool:
+    """True if every part allows a decode step to be captured in a CUDA graph."""
+    return (self.embedding.graph_safe and self.head.graph_safe and self.final_norm.graph_safe
+            and all(b.graph_safe for b in self.blocks.values()))
 
   # ---- caches ---------------------------------------------------------------
   def cache_needs(self) -> dict[str, Any]:

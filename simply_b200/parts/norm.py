@@ -19,6 +19,8 @@ from simply_b200.weights.loader import TensorSpec
 @NORMS.register("rms_norm")
 class RMSNorm(Norm):
 
+  graph_safe = True
+
   def __init__(self, prefix: str, width: int, eps: float, plus_one: bool = True):
     self.name = f"{prefix}.weight"
     self.width = width

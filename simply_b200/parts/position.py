@@ -19,6 +19,8 @@ from simply_b200.registry import POSITION_ENCODINGS
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEncoding(PositionEncoding):
 
+  graph_safe = True
+
   def __init__(self, prefix: str = "", theta: float = 10000.0, scale_factor: float = 1.0):
     self.theta = float(theta)
     self.scale_factor = float(scale_factor)
@@ -46,6 +48,8 @@ class RotaryEncoding(PositionEncoding):
 
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
+
+  graph_safe = True
 
   def __init__(self, prefix: str = ""):
     pass

@@ -1,7 +1,7 @@
 """Name -> class/function registries.
 
-Every pluggable thing in the engine (architectures, mixers, feed-forwards,
-norms, position encodings, block arrangements, activations) lives in one of
+Every pluggable thing in the engine (architectures, embeddings, output layers, mixers,
+feed-forwards, norms, position encodings, block arrangements, activations) lives in one of
 these registries under a string name.  A model description refers to parts by
 name only, so a new part is added by registering it; no framework file has to
 change.
@@ -62,6 +62,8 @@ class Registry(Generic[T]):
 
 # One registry per kind of part.  Values are classes (parts) or callables.
 ARCHITECTURES: Registry[Any] = Registry("architecture")
+EMBEDDINGS: Registry[Any] = Registry("embedding")
+HEADS: Registry[Any] = Registry("head")
 MIXERS: Registry[Any] = Registry("mixer")
 FEED_FORWARDS: Registry[Any] = Registry("feed_forward")
 NORMS: Registry[Any] = Registry("norm")

@@ -5,9 +5,16 @@ Field names and meanings follow the reference's `SamplingParams`
 (simply/serving/common_flags.py:76-84): `temperature` (0 means greedy,
 sampling_lib.py:494-497), `top_k` (-1 = whole vocabulary; 1 means greedy),
 `top_p` (1.0 = off), `max_decode_steps`.  `seed` is this engine's: every request
-draws from its own counter-based generator, so its tokens do not depend on what
-else is in the batch (the reference splits one global key per step,
-simply/utils/ragged_paged_attention.py:2031).
+draws from its own counter-based generator, keyed by (seed, position of the
+sampled token), so its tokens do not depend on what else is in the batch (the
+reference splits one global key per step, simply/utils/ragged_paged_attention.py:2031,
+which also makes the rows of a batch independent of each other).  A request
+given an explicit seed is reproducible: the same prompt, parameters and seed
+give the same tokens, in any batch.  With `seed=None` (the default) the engine
+derives a seed from the order in which it received the request, so that two
+requests with the same prompt draw different samples, as rows of the
+reference's batch do; `logprobs=True` also returns the log-probability of each
+emitted token (simply/utils/sampling_lib.py:540-601).
 """
 
 from __future__ import annotations
@@ -21,7 +28,7 @@ class SamplingParams:
   top_k: int = -1
   top_p: float = 1.0
   max_decode_steps: int = 256
-  seed: int = 0
+  seed: int | None = None
   # Token ids that end the request when sampled; None means the model's eos ids.
   stop_token_ids: tuple[int, ...] | None = None
 

@@ -59,8 +59,10 @@ def write_model_folder(
     matrix_std: float = 0.02,
     scale_std: float = 0.0,
     dtype: str = "bfloat16",
+    device: torch.device | str = "cpu",
 ) -> str:
-  """Writes config.json and model.safetensors for `config` (an architecture config object)."""
+  """Writes config.json and model.safetensors for `config` (an architecture config object).
+  `device` is where the values are drawn (each device's generator has its own sequence)."""
   from simply_b200.parts.model import tensor_specs  # parts import weights.loader; avoid a cycle
 
   if dtype not in _TORCH_DTYPES:
@@ -68,7 +70,8 @@ def write_model_folder(
   os.makedirs(out_dir, exist_ok=True)
   tensors = random_tensors(
       tensor_specs(config.model_spec()), seed, matrix_std=matrix_std, scale_std=scale_std,
-      dtype=_TORCH_DTYPES[dtype])
+      dtype=_TORCH_DTYPES[dtype], device=device)
+  tensors = {name: t.cpu() for name, t in tensors.items()}
   with open(os.path.join(out_dir, "config.json"), "w") as f:
     json.dump(config.to_dict(), f, indent=1)
   st.write_file(

@@ -173,7 +173,7 @@ def read_model_folder(model_dir, dtype=np.float32):
   tensors = {}
   with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
     for name in f.keys():
-      tensors[name] = f.get_tensor(name).double().numpy().astype(dtype)
+      tensors[name] = f.get_tensor(name).float().numpy().astype(dtype, copy=False)
   return cfg, tensors
 
 

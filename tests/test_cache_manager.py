@@ -155,3 +155,100 @@ def test_random_orders_keep_the_books_straight(seed):
     m.release_slot(slot)
   m.check_invariants()
   assert all(g.pool.num_free == g.pool.num_pages for g in m.groups)
+
+
+def test_a_window_group_gets_a_pool_of_its_own():
+  """The layer shapes of the largest named configuration, 64 requests of 8192 tokens, pages of 64:
+  the group that keeps everything needs 64 * 128 pages, the window group only what 64 windows,
+  a burst of decoded tokens and one step's prompt tokens can hold (the reference's
+  global_total_num_pages and local_total_num_pages, simply/serving/page_server.py:175-196)."""
+  needs = {"global": PagedKVNeed(16, 128, None), "local": PagedKVNeed(16, 128, 4096)}
+  m = CacheManager(needs, page_size=64, max_slots=64, max_seq_len=8192, max_cache_tokens=64 * 8192,
+                   device=None, step_tokens=2048, burst_tokens=16)
+  sizes = {g.window: g.pool.num_pages for g in m.groups}
+  assert sizes[None] == 64 * 128
+  assert sizes[4096] == 64 * (-(-(4095 + 16) // 64) + 2) + 2048 // 64 == 4320
+  # full size when asked for, an explicit size when given, never more than the full pool
+  full = CacheManager(needs, page_size=64, max_slots=64, max_seq_len=8192, max_cache_tokens=64 * 8192, device=None)
+  assert [g.pool.num_pages for g in full.groups] == [8192, 8192]
+  fixed = CacheManager(needs, page_size=64, max_slots=64, max_seq_len=8192, max_cache_tokens=64 * 8192,
+                       device=None, step_tokens=2048, windowed_cache_tokens=640)
+  assert {g.window: g.pool.num_pages for g in fixed.groups} == {None: 8192, 4096: 10}
+  small = CacheManager(needs, page_size=64, max_slots=64, max_seq_len=8192, max_cache_tokens=6400,
+                       device=None, step_tokens=2048)
+  assert [g.pool.num_pages for g in small.groups] == [100, 100]
+  # storage follows the group's own size
+  tiny = CacheManager({"g": PagedKVNeed(1, 8, None), "l": PagedKVNeed(2, 8, 5)}, page_size=4, max_slots=2,
+                      max_seq_len=64, max_cache_tokens=128, device="cpu", step_tokens=8)
+  assert tiny.paged["g"].storage.shape == (32, 2, 1, 4, 8)
+  assert tiny.paged["l"].storage.shape == (2 * (2 + 2) + 2, 2, 2, 4, 8)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_the_window_pool_never_runs_out_before_the_full_pool(seed):
+  """Steps as the scheduler makes them (prompt portions that together stay under the step's token
+  budget, beside bursts of decoded tokens): whenever a step lacks pages, the group that keeps every
+  token lacks them too, so the smaller window pool costs no step."""
+  rng = np.random.default_rng(seed)
+  page = int(rng.choice([2, 4, 16]))
+  window = int(rng.integers(2, 40))
+  budget, burst, slots, max_len = int(rng.integers(4, 50)), int(rng.integers(1, 9)), 5, 400
+  needs = {"g": PagedKVNeed(1, 8, None), "l": PagedKVNeed(1, 8, window)}
+  m = CacheManager(needs, page_size=page, max_slots=slots, max_seq_len=max_len, max_cache_tokens=slots * max_len,
+                   device=None, step_tokens=budget, burst_tokens=burst)
+  assert m.groups[1].pool.num_pages < m.groups[0].pool.num_pages
+  live = []
+  for _ in range(600):
+    if m.num_free_slots and rng.random() < 0.2:
+      live.append(m.acquire_slot(object()))
+    if live and rng.random() < 0.05:
+      m.release_slot(live.pop(int(rng.integers(len(live)))))
+    entries, left = [], budget
+    for s in live:
+      room = max_len - m.length(s)
+      if rng.random() < 0.5:  # decoding: a burst
+        n = min(burst, room)
+      else:  # a prompt portion out of the step's budget
+        n = min(int(rng.integers(0, left + 1)), room)
+        left -= n
+      if n > 0:
+        entries.append((s, n))
+    if entries:
+      short_by_group = []
+      for g in m.groups:
+        back = take = 0
+        for s, n in entries:
+          b, t = g.plan(s, m.length(s), n)
+          back, take = back + b, take + t
+        short_by_group.append(take - back - g.pool.num_free)
+      assert short_by_group[1] <= max(short_by_group[0], 0)
+      if m.pages_short(entries) == 0:
+        m.extend(entries)
+    for s in [s for s in live if m.length(s) >= max_len]:
+      m.release_slot(s)
+      live.remove(s)
+    m.check_invariants()
+
+
+def test_a_need_with_a_rule_of_its_own_forms_a_group_of_its_own():
+  """Which pages may go back is the need's rule: a need defined here keeps the first page (a
+  'sink') and a window; the manager groups, sizes and releases by asking it."""
+  import dataclasses
+
+  @dataclasses.dataclass(frozen=True)
+  class KeepsEverySecondWindow(PagedKVNeed):
+    def group_key(self):
+      return ("coarse_window", self.window)
+
+    def first_needed_page(self, lengths, page_size):
+      # gives pages back only in runs of two
+      return super().first_needed_page(lengths, page_size) // 2 * 2
+
+  needs = {"a": PagedKVNeed(1, 8, 6), "b": KeepsEverySecondWindow(1, 8, 6)}
+  m = CacheManager(needs, page_size=2, max_slots=1, max_seq_len=64, max_cache_tokens=64, device=None)
+  assert len(m.groups) == 2
+  s = m.acquire_slot("r")
+  for _ in range(20):
+    m.extend([(s, 1)])
+    m.check_invariants()
+  assert m.groups[0].first_page[s] == (19 - 5) // 2 and m.groups[1].first_page[s] == (19 - 5) // 2 // 2 * 2

@@ -45,7 +45,7 @@ def test_replay_four_ways(models, tmp_path, which, dtype, page):
                           ops=ReferenceOps(getattr(torch, dtype)))
   trace_util.run_in_process(eng, steps, str(tmp_path))
   eng.cache.check_invariants()
-  assert eng.cache.min_free_pages() == eng.cache.num_pages  # every request was ended
+  assert eng.cache.all_pages_free()  # every request was ended
   cases.compare(trace_util.collect(steps, str(tmp_path), plain.cfg["vocab_size"]), requests, expected, dtype)
 
 
@@ -96,7 +96,7 @@ def test_preemption_gives_the_same_tokens(models):
   tight = tight_engine.generate(prompts, sp)
   assert [r.output_token_ids for r in tight] == [r.output_token_ids for r in roomy]
   assert sum(r.num_preemptions for r in tight) > 0
-  assert tight_engine.cache.min_free_pages() == tight_engine.cache.num_pages
+  assert tight_engine.cache.all_pages_free()
 
 
 def test_the_package_has_no_cpu_path():

@@ -129,7 +129,7 @@ def test_preemption_gives_the_same_tokens(folders):
   assert [r.output_token_ids for r in tight] == [r.output_token_ids for r in roomy]
   assert sum(r.num_preemptions for r in tight) > 0
   tight_engine.cache.check_invariants()
-  assert tight_engine.cache.min_free_pages() == tight_engine.cache.num_pages
+  assert tight_engine.cache.all_pages_free()
 
 
 @pytest.mark.parametrize("seed", list(range(8)))
@@ -158,7 +158,7 @@ def test_random_workloads_float32_equal_plain(folders, seed):
   eng.ops.check_errors()
   assert [r.output_token_ids for r in got] == want
   eng.cache.check_invariants()
-  assert eng.cache.min_free_pages() == eng.cache.num_pages
+  assert eng.cache.all_pages_free()
 
 
 def test_engine_refuses_without_cuda_kernels(monkeypatch):

@@ -73,7 +73,7 @@ def test_finish_reasons_and_freeing():
   assert (c.finish_reason, len(c.tokens)) == ("max_seq_len", 12)
   assert (d.finish_reason, d.output) == ("eos", [9, 7])  # its own stop ids replace the model's
   assert not s.has_unfinished() and cache.num_free_slots == 4
-  assert cache.min_free_pages() == cache.num_pages
+  assert cache.all_pages_free()
 
 
 def test_bad_requests_end_at_once():
@@ -118,7 +118,7 @@ def test_decode_takes_pages_from_the_youngest():
   for _ in range(40):
     run_step(cache, s)
   assert not s.has_unfinished()
-  assert cache.min_free_pages() == cache.num_pages
+  assert cache.all_pages_free()
 
 
 def test_a_request_that_can_never_fit_ends_with_out_of_pages():
@@ -127,7 +127,7 @@ def test_a_request_that_can_never_fit_ends_with_out_of_pages():
   for _ in range(4):
     run_step(cache, s)
   assert r.finish_reason == "out_of_pages" and r.output == [7]  # one token fit, the next page did not
-  assert cache.min_free_pages() == cache.num_pages and cache.num_free_slots == 4
+  assert cache.all_pages_free() and cache.num_free_slots == 4
 
 
 @pytest.mark.parametrize("seed", range(5))
@@ -143,4 +143,21 @@ def test_random_load_on_a_tiny_pool_finishes_and_loses_nothing(seed):
     assert steps < 2000, "the scheduler does not make progress"
   assert all(r.status is Status.FINISHED for r in reqs)
   assert all(r.finish_reason in ("max_decode_steps", "max_seq_len", "out_of_pages") for r in reqs)
-  assert cache.min_free_pages() == cache.num_pages and cache.num_free_slots == 3
+  assert cache.all_pages_free() and cache.num_free_slots == 3
+
+
+def test_a_window_pool_smaller_than_the_full_pool():
+  """The window group's pool is its own (and here deliberately scarce): the scheduler cuts portions
+  and preempts by the group that is short, and every request still ends with all pages back."""
+  cache = CacheManager({"g": PagedKVNeed(1, 8, None), "l": PagedKVNeed(1, 8, 8)}, page_size=4, max_slots=4,
+                       max_seq_len=64, max_cache_tokens=64 * 4, device=None, step_tokens=16,
+                       windowed_cache_tokens=10 * 4)
+  assert [g.pool.num_pages for g in cache.groups] == [64, 10]
+  s = Scheduler(cache, max_num_issue_tokens=16, max_seq_len=64)
+  reqs = [s.add(i, list(range(3 + 9 * i)), SamplingParams(temperature=0.0, max_decode_steps=12)) for i in range(5)]
+  for _ in range(400):
+    if not s.has_unfinished():
+      break
+    run_step(cache, s)
+  assert all(r.status is Status.FINISHED and r.finish_reason == "max_decode_steps" for r in reqs)
+  assert cache.all_pages_free() and cache.num_free_slots == 4

@@ -11,6 +11,7 @@ from simply_b200.config import load_config, preset
 from simply_b200.parts.model import DecoderModel, tensor_specs
 from simply_b200.weights import WeightError, load_tensors, random_tensors, write_model_folder
 from simply_b200.weights import safetensors_io as st
+from tests.reference_ops import ReferenceOps
 from tests.tiny_models import write_tiny
 
 
@@ -68,6 +69,30 @@ def test_dtype_rule(tmp_path):
   assert torch.equal(f32["model.norm.weight"], bf["model.norm.weight"].float())
 
 
+def test_a_folder_stored_in_float32_is_narrowed_to_the_activation_dtype(tmp_path, capsys):
+  """simply/utils/checkpoint_lib.py:658-670: wider floats are restored in the activation dtype.
+  Matrices become bfloat16 (and equal the bfloat16 folder's), norm scales stay as stored."""
+  narrow = write_tiny("a", tmp_path / "n", "bfloat16")
+  wide = write_tiny("a", tmp_path / "w", "float32")
+  specs = tensor_specs(load_config(wide).model_spec())
+  a = load_tensors(narrow, specs, torch.bfloat16, "cpu")
+  b = load_tensors(wide, specs, torch.bfloat16, "cpu")
+  assert "narrowed to bfloat16" in capsys.readouterr().err
+  for name, t in b.items():
+    if name.endswith("norm.weight") or "layernorm" in name:
+      assert t.dtype == torch.float32
+      assert torch.equal(t.to(torch.bfloat16), a[name])
+    else:
+      assert t.dtype == torch.bfloat16 and torch.equal(t, a[name]), name
+  kept = load_tensors(wide, specs, torch.bfloat16, "cpu", keep_float32=True)
+  assert all(t.dtype == torch.float32 for t in kept.values())
+  # a part may declare a matrix of its own as precision-critical
+  import dataclasses
+  name = "model.layers.0.mlp.down_proj.weight"
+  special = [dataclasses.replace(s, precision="stored") if s.name == name else s for s in specs]
+  assert load_tensors(wide, special, torch.bfloat16, "cpu")[name].dtype == torch.float32
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
   folder = write_tiny("a", tmp_path, "bfloat16")
   specs = tensor_specs(load_config(folder).model_spec())
@@ -102,7 +127,14 @@ def test_tied_table_may_be_repeated_as_lm_head(tmp_path):
   reader.close()
   tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
   st.write_file(os.path.join(folder, "model.safetensors"), tensors)
-  load_tensors(folder, specs, torch.bfloat16, "cpu")
+  loaded = load_tensors(folder, specs, torch.bfloat16, "cpu")
+  DecoderModel(load_config(folder).model_spec()).bind(loaded, ReferenceOps(torch.bfloat16))  # a copy: accepted
+  # ... but not another table under that name
+  tensors["lm_head.weight"][3, 5] += 1.0
+  st.write_file(os.path.join(folder, "model.safetensors"), tensors)
+  loaded = load_tensors(folder, specs, torch.bfloat16, "cpu")
+  with pytest.raises(WeightError, match="lm_head.weight differs"):
+    DecoderModel(load_config(folder).model_spec()).bind(loaded, ReferenceOps(torch.bfloat16))
 
 
 def test_broken_files(tmp_path):
