@@ -4,12 +4,19 @@
 
 Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with every
 sequence ending at the full context (8,192 cached tokens), timed on the device over K
-decode steps that run back to back from CUDA graphs.  `e2e` is the same through the
+decode steps that run back to back from CUDA graphs; the figure is the median of five
+such bursts of K steps, each bracketed by events of its own (the last burst ends at the
+full context, the first 4 K tokens before it).  `e2e` is the same through the
 public entry point (`Engine.add_request` / `Engine.step`), host tokens in and out, one
 host round trip per step.  `prefill` is one 2,048-token prompt in one step; `points`
-holds decode at batch 1 and 64 and a serving-like run through `Engine.generate` (128
-requests over 64 slots, prompts of about 512 and outputs of about 128 tokens); `roofline` relates the decode step's bytes (every weight
-once, plus the cache of the live requests) to the measured copy bandwidth.
+holds decode at batch 1 and 64 (other presets: the batches their configuration names), at
+batch 8 with contexts of 1,024 and 4,096, and a serving-like run through `Engine.generate` (128
+requests over 64 slots, prompts of about 512 and outputs of about 128 tokens); `roofline`
+relates the decode step's bytes (every weight once, plus the cache of the live requests) to the
+measured copy bandwidth; `kernels` gives the dominant kernels' own fractions, each timed alone
+over all layers' weights or caches: the weight-streaming products and the split-key attention of
+a decode step (of the copy bandwidth), the gate-up product with its activation of a 2,048-token
+prefill (of the matrix-product peak).
 
 A step reads 5.2 GB of weights and 0.65 GB of cache per sequence, far more than the
 126 MB L2, so no L2 flush is needed between timed steps ("inputs larger than L2").
@@ -177,15 +184,20 @@ def settle(torch, seconds=0.5):
   time.sleep(seconds)
 
 
-def time_decode(engine, torch, batch, context, steps, warmup, seed):
-  """Device time of `steps` decode steps at `batch`, the last one ending at `context` cached
-  tokens.  Returns (ms per step, kernel launches per step)."""
+BURSTS = 5  # timed bursts per decode point; the median is reported
+
+
+def time_decode(engine, torch, batch, context, steps, warmup, seed, bursts=BURSTS):
+  """Device time of a burst of `steps` decode steps at `batch`: the median of `bursts` bursts
+  that follow one another, the last one ending at `context` cached tokens.  Returns (ms per
+  step, kernel launches per step, [ms per step of every burst])."""
   import numpy as np
   from simply_b200 import StepEntry
 
   rng = np.random.default_rng(seed)
   vocab = engine.model.spec.vocab_size
-  start = context - steps - warmup
+  bursts = max(1, min(bursts, (context - warmup - 1) // steps))
+  start = context - bursts * steps - warmup
   slots = [engine.open_request(f"bench{seed}_{i}") for i in range(batch)]
   chunk = 2048
   for slot in slots:
@@ -201,20 +213,108 @@ def time_decode(engine, torch, batch, context, steps, warmup, seed):
   last = rng.integers(0, vocab, batch).tolist()
   toks = runner.run(slots, last, params, warmup)  # captures the graph, warms up
   params[:, 5] += warmup
-  # Timed: `steps` replays back to back; events bracket exactly these.
-  torch.cuda.synchronize()
-  launches0 = engine.ops.launches
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  e0.record()
-  toks = runner.run(slots, toks[-1].tolist(), params, steps)
-  e1.record()
-  torch.cuda.synchronize()
-  ms = e0.elapsed_time(e1) / steps
-  launches = (engine.ops.launches - launches0) / steps
+  # Timed: `steps` replays back to back, `bursts` times; events bracket exactly one burst each.
+  per_burst = []
+  launches = 0.0
+  for _ in range(bursts):
+    torch.cuda.synchronize()
+    launches0 = engine.ops.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    toks = runner.run(slots, toks[-1].tolist(), params, steps)
+    e1.record()
+    torch.cuda.synchronize()
+    per_burst.append(e0.elapsed_time(e1) / steps)
+    launches = (engine.ops.launches - launches0) / steps
+    params[:, 5] += steps
   engine.ops.check_errors()
   for slot in slots:
     engine.close_request(slot)
-  return ms, launches
+  return float(np.median(per_burst)), launches, per_burst
+
+
+def time_kernels(engine, torch, cfg, batch, context, peaks):
+  """The dominant kernels on their own, each over all layers in a row so that every launch
+  streams its own weights or its own cache from memory (5 GB of weights, 5 GB of cache: far
+  more than L2): the four products of a decode step, the attention of a decode step, and the
+  gate-up product with its activation for a 2,048-token prompt.  Median of 5, device-timed."""
+  import numpy as np
+  from simply_b200 import StepEntry
+
+  ops, dev = engine.ops, engine.device
+  blocks = list(engine.model.blocks.values())
+
+  def timed(fn, reps=5):
+    fn()
+    times = []
+    for _ in range(reps):
+      torch.cuda.synchronize()
+      e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      e0.record()
+      fn()
+      e1.record()
+      torch.cuda.synchronize()
+      times.append(e0.elapsed_time(e1))
+    return float(np.median(times))
+
+  out = {}
+  d, hq, dh, f = cfg.hidden_size, cfg.num_attention_heads, cfg.head_dim, cfg.intermediate_size
+  x_d = torch.randn(batch, d, device=dev).to(torch.bfloat16)
+  x_o = torch.randn(batch, hq * dh, device=dev).to(torch.bfloat16)
+  x_f = torch.randn(batch, f, device=dev).to(torch.bfloat16)
+
+  def products():
+    for b in blocks:
+      ops.linear(x_d, b.mixer.qkv_weight)
+      ops.linear(x_o, b.mixer.o_proj.weight)
+      ops.gated_linear(x_d, b.feed_forward.gate_up_weight, b.feed_forward.activation)
+      ops.linear(x_f, b.feed_forward.down_proj.weight)
+
+  with ops.hold_stream():
+    ms = timed(products)
+  weight_bytes = sum(w.numel() * 2 for b in blocks for w in (
+      b.mixer.qkv_weight, b.mixer.o_proj.weight, b.feed_forward.gate_up_weight, b.feed_forward.down_proj.weight))
+  gbs = weight_bytes / (ms * 1e-3) / 1e9
+  out[f"decode_products_b{batch}"] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4)}
+
+  # Attention of a decode step: the cache is made to hold the context without computing it
+  # (the kernel's time does not depend on what the pages hold).
+  slots = [engine.open_request(f"k{i}") for i in range(batch)]
+  for s in slots:
+    engine.cache.extend([(s, context - 1)])
+  ctx = engine._prepare([StepEntry(s, [0], (0,)) for s in slots])
+  q = torch.randn(batch, hq, dh, device=dev).to(torch.bfloat16)
+  calls = [(engine.caches[name], engine.model.blocks[call.layer].mixer)
+           for call, name in zip(engine.model.spec.run_order, engine.model.cache_names)]
+
+  def attention():
+    for cache, m in calls:
+      ops.paged_attention(q, cache.storage, ctx.block_tables[cache.group], ctx, num_heads=m.num_heads,
+                          num_kv_heads=m.num_kv_heads, head_dim=m.head_dim, logit_softcap=m.logit_softcap,
+                          window=m.window)
+
+  with ops.hold_stream():
+    ms = timed(attention)
+  kv_bytes = decode_bytes(cfg, len(blocks), batch, context) - model_numbers(cfg, len(blocks))["weight_bytes"]
+  gbs = kv_bytes / (ms * 1e-3) / 1e9
+  out[f"decode_attention_b{batch}"] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4)}
+  ops.check_errors()
+  for s in slots:
+    engine.close_request(s)
+
+  tokens = 2048
+  x_p = torch.randn(tokens, d, device=dev).to(torch.bfloat16)
+
+  def gate_up():
+    for b in blocks:
+      ops.gated_linear(x_p, b.feed_forward.gate_up_weight, b.feed_forward.activation)
+
+  with ops.hold_stream():
+    ms = timed(gate_up)
+  tflops = 2 * tokens * d * 2 * f * len(blocks) / (ms * 1e-3) / 1e12
+  out[f"prefill_gate_up_{tokens}"] = {"ms": round(ms, 4), "tflops": round(tflops, 1),
+                                      "frac": round(tflops / peaks["bf16_tflops"], 4)}
+  return out
 
 
 def time_serving(engine, torch, cfg, requests=128, prompt=512, out=128):
@@ -337,10 +437,15 @@ def main(argv=None):
   if layers != full_layers:
     cfg = cfg.replace(num_hidden_layers=layers, layer_types=cfg.resolved_layer_types()[:layers])
   context = args.context or cfg.max_position_embeddings
-  max_batch = 8 if args.skip_points else 64
+  # The other decode points of each named configuration: (batch, context).  The largest model's
+  # batch of 64 runs at 2,048 cached tokens (its cache at 8,192 would not fit beside the weights).
+  point_table = {"gemma2-9b": ((1, context), (32, context)), "gemma2-27b": ((1, context), (64, min(context, 2048)))}
+  point_list = point_table.get(args.preset, ((1, context), (64, context)))
+  max_batch = 8 if args.skip_points else max(b for b, _ in point_list)
   max_batch = max(max_batch, args.batch)
+  cache_tokens = max([args.batch * context] + ([] if args.skip_points else [b * c for b, c in point_list]))
   ec = EngineConfig(activation_dtype="bfloat16", page_size=args.page_size, batch_size=max_batch, max_seq_len=context,
-                    max_cache_tokens=max_batch * context, max_num_issue_tokens=2048, intermediate_steps=1)
+                    max_cache_tokens=cache_tokens, max_num_issue_tokens=2048, intermediate_steps=1)
   t0 = time.time()
   engine = Engine.from_config(cfg, seed=0, engine_config=ec, matrix_std=0.02, scale_std=0.0)
   torch.cuda.synchronize()
@@ -353,7 +458,7 @@ def main(argv=None):
   sampler.start()
 
   # ---- decode, device-timed ----------------------------------------------------------
-  ms_step, launches = time_decode(engine, torch, args.batch, context, args.steps, args.warmup, seed=1)
+  ms_step, launches, bursts_ms = time_decode(engine, torch, args.batch, context, args.steps, args.warmup, seed=1)
   value = args.batch / (ms_step * 1e-3)
 
   # ---- end to end through the public entry point (next, while the GPU is in the same state) ---
@@ -386,12 +491,22 @@ def main(argv=None):
   e2e_value = args.batch * e2e_steps / e2e_s
 
   points = {}
+  kernels = {}
   if not args.skip_points:
-    for b in (1, 64):
-      ms_b, _ = time_decode(engine, torch, b, context, args.steps, args.warmup, seed=10 + b)
-      points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
-      points[f"decode_b{b}_ms"] = round(ms_b, 4)
-      points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, layers, b, context) / (ms_b * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+    for b, c in point_list:
+      ms_b, _, _ = time_decode(engine, torch, b, c, args.steps, args.warmup, seed=10 + b)
+      name = f"decode_b{b}" if c == context else f"decode_b{b}_ctx{c}"
+      points[name] = round(b / (ms_b * 1e-3), 1)
+      points[f"{name}_ms"] = round(ms_b, 4)
+      points[f"{name}_hbm_frac"] = round(decode_bytes(cfg, layers, b, c) / (ms_b * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+    for c in (1024, 4096):
+      if c < context:
+        ms_c, _, _ = time_decode(engine, torch, args.batch, c, args.steps, args.warmup, seed=20 + c)
+        name = f"decode_b{args.batch}_ctx{c}"
+        points[name] = round(args.batch / (ms_c * 1e-3), 1)
+        points[f"{name}_ms"] = round(ms_c, 4)
+        points[f"{name}_hbm_frac"] = round(decode_bytes(cfg, layers, args.batch, c) / (ms_c * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+    kernels = time_kernels(engine, torch, cfg, args.batch, context, peaks)
 
   # ---- prefill: one 2,048-token prompt in one step --------------------------------------
   rng = np.random.default_rng(5)
@@ -421,12 +536,13 @@ def main(argv=None):
     points.update(time_serving(engine, torch, cfg))
     engine.scheduler.max_num_issue_tokens = budget
 
+  metric_name = {"gemma2-2b": "Gemma 2 2B", "gemma2-9b": "Gemma 2 9B", "gemma2-27b": "Gemma 2 27B"}.get(args.preset, args.preset)
   clocks = sampler.stop()
   step_bytes = decode_bytes(cfg, layers, args.batch, context)
   achieved = step_bytes / (ms_step * 1e-3) / 1e9
   n = model_numbers(cfg, layers)
   out = {
-      "metric": "decode tok/s @ batch 8, 8192-token context (Gemma 2 2B, 1 B200)",
+      "metric": f"decode tok/s @ batch {args.batch}, {context}-token context ({metric_name}, 1 B200)",
       "value": round(value, 1),
       "unit": "tokens/s",
       "n_gpus": 1,
@@ -445,7 +561,9 @@ def main(argv=None):
           "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size, "window": cfg.sliding_window,
           "global_batch": args.batch, "seq_len": context, "page_size": args.page_size, "parallelism": "1 GPU",
           "l2": "inputs larger than L2", "peaks": peaks_from, "params": n["params"],
+          "timed": f"median of {len(bursts_ms)} bursts of {args.steps} steps",
       },
+      "bursts_ms_per_step": [round(b, 4) for b in bursts_ms],
       "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
               "d2h_bytes_per_step": d2h, "steps": e2e_steps},
       "gpu_launches": int(round(launches * args.steps)),
@@ -453,6 +571,7 @@ def main(argv=None):
       "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                    "frac": round(achieved / peaks["hbm_gbs"], 4)},
       "points": points,
+      "kernels": kernels,
       "clocks": clocks,
       "setup_s": round(setup_s, 1),
   }

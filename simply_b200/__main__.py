@@ -47,6 +47,7 @@ flags.DEFINE_integer("intermediate_steps", 1, "Decode steps that run in a row wi
 flags.DEFINE_integer("max_num_issue_tokens", 0, "Token budget of one step; 0 means 2048.")
 flags.DEFINE_integer("seed", 0, "Sampling seed; request i samples with seed + i.")
 flags.DEFINE_bool("use_cuda_graphs", True, "Replay decode steps from CUDA graphs.")
+flags.DEFINE_bool("logprobs", False, "Also print the log-probability of every output token.")
 flags.DEFINE_string("prompt_ids", None, "Prompts as token ids: '1,2,3;4,5' (';' separates prompts).")
 flags.DEFINE_string("prompt_file", None, "File with one prompt per line: token ids separated by spaces or commas.")
 
@@ -110,12 +111,15 @@ def main(argv):
   else:
     raise app.UsageError("give --ckpt_dir, or --experiment_config with --random_weights")
   params = [SamplingParams(temperature=FLAGS.temperature, top_k=FLAGS.top_k, top_p=FLAGS.top_p,
-                           max_decode_steps=FLAGS.max_decode_steps, seed=FLAGS.seed + i)
+                           max_decode_steps=FLAGS.max_decode_steps, seed=FLAGS.seed + i, logprobs=FLAGS.logprobs)
             for i in range(len(prompts))]
   for r in engine.generate(prompts, params):
-    print(json.dumps({"request_id": r.request_id, "input_token_ids": r.input_token_ids,
-                      "output_token_ids": r.output_token_ids, "finish_reason": r.finish_reason,
-                      "is_truncated": r.is_truncated}))
+    line = {"request_id": r.request_id, "input_token_ids": r.input_token_ids,
+            "output_token_ids": r.output_token_ids, "finish_reason": r.finish_reason,
+            "is_truncated": r.is_truncated}
+    if FLAGS.logprobs:
+      line["output_token_logprobs"] = r.output_token_logprobs
+    print(json.dumps(line))
   return 0
 
 

@@ -194,6 +194,7 @@ class CacheManager:
         raise TypeError(f"cache {name!r}: unknown kind of need {need!r}")
     self.lengths = np.zeros(max_slots, dtype=np.int64)
     self.owner: list[object | None] = [None] * max_slots
+    self._live = np.zeros(max_slots, dtype=bool)  # owner is not None
     self._free_slots = list(range(max_slots - 1, -1, -1))
 
   # ---- slots ----------------------------------------------------------------
@@ -206,6 +207,7 @@ class CacheManager:
       raise RuntimeError("no free slot")
     slot = self._free_slots.pop()
     self.owner[slot] = owner
+    self._live[slot] = True
     self.lengths[slot] = 0
     for s in self.states.values():
       if s.storage is not None:
@@ -219,6 +221,7 @@ class CacheManager:
     for gi, g in enumerate(self.groups):
       self._poison(gi, g.release_slot(slot))
     self.owner[slot] = None
+    self._live[slot] = False
     self.lengths[slot] = 0
     self._free_slots.append(slot)
 
@@ -242,13 +245,31 @@ class CacheManager:
         return False
     return True
 
+  def _idle_releasable(self, g: PageGroup, busy: set[int]) -> list[tuple[int, int]]:
+    """(slot, pages) of live requests outside the step that hold pages no later query of theirs
+    can see (what their last portion left below the window).  Such pages go back whenever a step
+    has to take pages, so that a request that waits never keeps more than its window."""
+    if g.window is None and type(g.need) is PagedKVNeed:
+      return []  # keeps every token
+    live = self._live.copy()
+    if busy:
+      live[list(busy)] = False
+    idx = np.nonzero(live)[0]
+    if idx.size == 0:
+      return []
+    first = np.minimum(g.need.first_needed_page(self.lengths[idx], self.page_size), g.end_page[idx])
+    extra = first - g.first_page[idx]
+    return [(int(s), int(n)) for s, n in zip(idx, extra) if n > 0]
+
   def pages_short(self, entries: Sequence[tuple[int, int]]) -> int:
     """How many pages the batch `[(slot, new tokens)]` lacks (0 if it fits), worst group."""
     if self.changes_no_table(entries):
       return 0
     short = 0
+    busy = {slot for slot, _ in entries}
     for g in self.groups:
-      back = take = 0
+      take = 0
+      back = sum(n for _, n in self._idle_releasable(g, busy))
       for slot, n in entries:
         b, t = g.plan(slot, int(self.lengths[slot]), n)
         back += b
@@ -298,7 +319,11 @@ class CacheManager:
     if short:
       raise OutOfPages(f"the step lacks {short} page(s)")
     for gi, g in enumerate(self.groups):
-      # Every slot gives back before any slot takes, as the pool may need those pages.
+      # Every slot gives back before any slot takes, as the pool may need those pages: first the
+      # requests outside the step, then the step's own.
+      for slot, _ in self._idle_releasable(g, seen):
+        back, _ = g.apply(slot, int(self.lengths[slot]), 0)
+        self._poison(gi, back)
       for slot, n in entries:
         cur = int(self.lengths[slot])
         n_back, _ = g.plan(slot, cur, 0)
@@ -339,8 +364,8 @@ class CacheManager:
             raise AssertionError(
                 f"slot {slot}: {int(g.end_page[slot])} pages end for {length} tokens")
           if length > 0:
-            # Everything the last cached token can see must still be held.
-            needed = int(g.need.first_needed_page(np.array([length - 1]), self.page_size)[0])
+            # Everything the request's next query can see must still be held.
+            needed = int(g.need.first_needed_page(np.array([length]), self.page_size)[0])
             if int(g.first_page[slot]) > needed:
               raise AssertionError(f"slot {slot}: pages that are still visible were given back")
         held.extend(pages)

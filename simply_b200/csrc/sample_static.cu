@@ -40,7 +40,11 @@ extern "C" int sb_sample_static(const float* logits, const int* params, int* out
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
-  if (device < 0 || device >= SB_MAX_DEVICES) return SB_SAMPLE_STATIC_BAD_ARGUMENT;
+  if (device < 0 || device >= SB_MAX_DEVICES) {
+    fprintf(stderr, "sb_sample_static: device ordinal %d is beyond the %d this entry point keeps addresses for\n",
+            device, SB_MAX_DEVICES);
+    return SB_SAMPLE_STATIC_BAD_ARGUMENT;
+  }
   if (g_scratch_address[device] == nullptr) {
     // Once per device, with that device current (it is: we just asked which one is).
     void* address = nullptr;

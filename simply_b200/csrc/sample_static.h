@@ -32,7 +32,12 @@
  *
  * Returns 0 on success, a positive cudaError_t if a CUDA call failed, or
  *   SB_SAMPLE_STATIC_TOO_MANY_ROWS   num_rows > SB_SAMPLE_STATIC_MAX_ROWS
- *   SB_SAMPLE_STATIC_BAD_ARGUMENT    a null pointer, num_rows < 0 or vocab <= 0
+ *   SB_SAMPLE_STATIC_BAD_ARGUMENT    a null pointer, num_rows < 0 or vocab <= 0; the current
+ *                                    device's ordinal is 64 or more (the table of per-device
+ *                                    addresses ends there); or the sampling kernels would cut a
+ *                                    row into more than SB_SAMPLE_STATIC_MAX_SLICES slices (they
+ *                                    never do: sb_sample_slices caps at the same number, and a
+ *                                    static_assert in sampling.cu ties the two together)
  * (a line that names the limit is also written to stderr).
  */
 #ifndef SIMPLY_B200_SAMPLE_STATIC_H_

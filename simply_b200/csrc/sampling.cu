@@ -18,6 +18,13 @@
 #include <float.h>
 
 #include "common.cuh"
+#include "sample_static.h"
+
+// Most slices a row of the vocabulary is cut into.  The static scratch of sb_sample_static is
+// laid out for this many partial results per row.
+#define SAMPLE_MAX_SLICES 64
+static_assert(SAMPLE_MAX_SLICES == SB_SAMPLE_STATIC_MAX_SLICES,
+              "sb_sample_static's scratch holds SB_SAMPLE_STATIC_MAX_SLICES partial results per row");
 
 #define SAMPLE_THREADS 1024
 
@@ -239,10 +246,64 @@ __global__ void sample_final_kernel(const ArgMax* __restrict__ partial, int* __r
   if (lane == 0) out[r] = best.i;
 }
 
+// Log-probability of the token that was drawn, under the distribution it was drawn from
+// (simply/utils/sampling_lib.py:540-601): 0 when the row is greedy; otherwise the log-softmax of
+// logits / temperature over the entries the masks keep, at the token.  One block per row; reads
+// the keep-thresholds that sample_threshold_kernel left in the scratch of the same sb_sample call.
+// With `step_counter` the result goes to row *step_counter of `out` (a burst's history).
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_logprob_kernel(const float* __restrict__ logits, const int* __restrict__ params,
+                      const uint32_t* __restrict__ thresholds, const int* __restrict__ tokens,
+                      float* __restrict__ out, const int* __restrict__ step_counter, int vocab) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  __shared__ float fscratch[33];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const int* p = params + r * 6;
+  const float temperature = __int_as_float(p[0]);
+  const int top_k = p[1];
+  float* dst = out + (step_counter ? (size_t)*step_counter * gridDim.x : 0) + r;
+  if (temperature == 0.f || top_k == 1) {
+    if (threadIdx.x == 0) *dst = 0.f;
+    return;
+  }
+  const uint32_t threshold = thresholds[r];
+  float mx = -FLT_MAX;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float s = row[i] / temperature;
+    if (order_key(s) >= threshold) mx = fmaxf(mx, s);
+  }
+  mx = block_max(mx, fscratch);
+  float z = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float s = row[i] / temperature;
+    if (order_key(s) >= threshold) z += expf(s - mx);
+  }
+  z = block_sum(z, fscratch);
+  if (threadIdx.x == 0) {
+    const int tok = tokens[r];
+    const float s = (tok >= 0 && tok < vocab) ? row[tok] / temperature : -FLT_MAX;
+    *dst = order_key(s) >= threshold ? s - mx - logf(z) : -FLT_MAX;
+  }
+}
+
+// After sb_sample with the same arguments and scratch: out[r] (or out[*step_counter, r]) is the
+// log-probability of tokens[r].
+extern "C" int sb_sample_logprobs(const float* logits, const int* params, const int* tokens, float* out,
+                                  const int* step_counter, int num_rows, int vocab, const void* scratch,
+                                  cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  sb_launch(sample_logprob_kernel, num_rows, SAMPLE_THREADS, 0, stream, logits, params,
+            reinterpret_cast<const uint32_t*>(scratch), tokens, out, step_counter, vocab);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
 // scratch: at least num_rows * (1 + 2 * slices) 32-bit words, slices = sb_sample_slices(num_rows, vocab).
 extern "C" int sb_sample_slices(int num_rows, int vocab) {
   int slices = (4 * 148 + num_rows - 1) / (num_rows > 0 ? num_rows : 1);
-  if (slices > 64) slices = 64;
+  if (slices > SAMPLE_MAX_SLICES) slices = SAMPLE_MAX_SLICES;
   const int most = (vocab + 1023) / 1024;  // at least about a thousand entries per slice
   if (slices > most) slices = most;
   return slices < 1 ? 1 : slices;

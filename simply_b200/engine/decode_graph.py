@@ -58,6 +58,7 @@ class _Graph:
   bucket: int
   launches: int
   logits_history: torch.Tensor | None = None  # [MAX_BURST, batch, vocab] when logits are kept
+  logprob_history: torch.Tensor | None = None  # [MAX_BURST, batch] when the graph computes log-probabilities
   resume: dict | None = None  # what the device holds after the last burst (see DecodeRunner.run)
   graph_exec: Any = None  # the instantiated graph's handle and the buffers' addresses, for the native launch
   pointers: tuple = ()
@@ -70,7 +71,8 @@ class DecodeRunner:
   def __init__(self, engine: Any):
     self.engine = engine
     self.ops = engine.ops
-    self.graphs: dict[tuple[int, int], _Graph] = {}
+    self.graphs: dict[tuple[int, int, bool], _Graph] = {}
+    self.last_logprobs: np.ndarray | None = None  # [steps, live] after a burst run with logprobs
     # True keeps the float32 logits of every step of a burst on the device (`last_logits` after
     # `run`): tests compare the rows a replay produced with a plain model's.  Set before the
     # first burst; costs MAX_BURST * batch * vocab floats per graph.
@@ -126,8 +128,9 @@ class DecodeRunner:
       take(f"plan{i}", plan.words)
     return views, off
 
-  def _prepare(self, batch: int, bucket: int) -> _Graph:
-    """Static buffers and the step closure for one (batch, bucket); nothing runs yet."""
+  def _prepare(self, batch: int, bucket: int, logprobs: bool = False) -> _Graph:
+    """Static buffers and the step closure for one (batch, bucket); nothing runs yet.  With
+    `logprobs` the step also records the log-probability of every sampled token."""
     eng, ops = self.engine, self.ops
     plan_list = self._plans(batch, bucket)
     views, words = self._layout(batch, bucket, plan_list)
@@ -155,17 +158,22 @@ class DecodeRunner:
       logits_history = torch.zeros(self.MAX_BURST, batch, eng.model.spec.vocab_size, dtype=torch.float32,
                                    device=eng.device)
 
+    logprob_history = None
+    if logprobs:
+      logprob_history = torch.zeros(self.MAX_BURST, batch, dtype=torch.float32, device=eng.device)
+
     def one_step():
       ctx.memo = dict(bound)
       logits = eng.model.forward(ctx, eng.caches)
       if logits_history is not None:
         ops.keep_logits(logits, logits_history, view("step_counter"))
-      ops.sample_device(logits, view("sample_params").view(batch, 6), sampled)
+      ops.sample_device(logits, view("sample_params").view(batch, 6), sampled, logprobs_out=logprob_history,
+                        step_counter=view("step_counter") if logprobs else None)
       ops.decode_advance(sampled, view("token_ids"), view("positions"), view("q_start"),
                          view("sample_params"), history, view("step_counter"))
 
     g = _Graph(torch.cuda.CUDAGraph(), meta, host, views, plans, sampled, history, host_history, one_step,
-               False, batch, bucket, 0, logits_history)
+               False, batch, bucket, 0, logits_history, logprob_history)
     self._fill_constants(g)
     return g
 
@@ -220,8 +228,9 @@ class DecodeRunner:
     return all(len(x) == len(y) and all(np.array_equal(p, q) for p, q in zip(x, y)) for x, y in zip(a, b))
 
   def run(self, slots: Sequence[int], last_tokens: Sequence[int], sample_params: np.ndarray,
-          steps: int) -> np.ndarray:
-    """Decodes `steps` tokens for every slot; returns the sampled tokens [steps, batch].
+          steps: int, logprobs: bool = False) -> np.ndarray:
+    """Decodes `steps` tokens for every slot; returns the sampled tokens [steps, batch].  With
+    `logprobs`, `last_logprobs` [steps, batch] then holds the tokens' log-probabilities.
 
     `last_tokens[i]` is the not yet cached last token of slot i; `sample_params` is the
     [batch, 6] word table of csrc/sampling.cu with the position of the first token to sample.
@@ -248,10 +257,10 @@ class DecodeRunner:
     bucket = 1024
     while bucket < int(lengths.max()) + steps:
       bucket *= 2
-    key = (batch, bucket)
+    key = (batch, bucket, bool(logprobs))
     g = self.graphs.get(key)
     if g is None:
-      g = self.graphs[key] = self._prepare(batch, bucket)
+      g = self.graphs[key] = self._prepare(batch, bucket, bool(logprobs))
     # What the device would need to be told.  If it is exactly what the last burst of this graph
     # left behind (same requests one step on, no page taken or given back, the same key chunks),
     # the device's own copy, advanced by the graph itself, is already right: only the tokens are
@@ -332,6 +341,8 @@ class DecodeRunner:
     out = g.host_history[rows].numpy()[:, :live].copy()
     if g.logits_history is not None:
       self.last_logits = g.logits_history[rows, :live].clone()
+    if g.logprob_history is not None:
+      self.last_logprobs = g.logprob_history[rows, :live].cpu().numpy()
     self.ops.launches += g.launches * replays
     eng.num_steps += steps
     return out

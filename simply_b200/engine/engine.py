@@ -42,6 +42,9 @@ class GenerationResult:
   output_token_ids: list[int]
   finish_reason: str
   num_preemptions: int = 0
+  # With SamplingParams(logprobs=True): log-probability of every output token under the
+  # distribution it was drawn from (the reference's `output_token_logprobs`).
+  output_token_logprobs: list[float] | None = None
 
   @property
   def is_truncated(self) -> bool:
@@ -227,17 +230,22 @@ class Engine:
         samplers.append(r)
     logits = self.step_raw(entries)
     sampled: dict[object, int] = {}
+    logprobs: dict[object, float] | None = None
     if samplers:
+      want_logprobs = any(r.params.logprobs for r in samplers)
       tokens = self.ops.sample(
           logits,
           [r.params.temperature for r in samplers],
           [r.params.top_k for r in samplers],
           [r.params.top_p for r in samplers],
           [r.params.seed for r in samplers],
-          [len(r.tokens) for r in samplers])
+          [len(r.tokens) for r in samplers], **({"logprobs": True} if want_logprobs else {}))
+      if want_logprobs:
+        tokens, lp = tokens
+        logprobs = {r.request_id: v for r, v in zip(samplers, lp.tolist())}
       for r, t in zip(samplers, tokens.tolist()):
         sampled[r.request_id] = t
-    return finished + self.scheduler.commit(plan, sampled)
+    return finished + self.scheduler.commit(plan, sampled, logprobs)
 
   def _decode_burst(self, plan: StepPlan) -> list[Request]:
     """A step (or `intermediate_steps` steps in a row) in which every entry decodes one token,
@@ -254,15 +262,21 @@ class Engine:
         [r.params.temperature for r in requests], [r.params.top_k for r in requests],
         [r.params.top_p for r in requests], [r.params.seed for r in requests],
         [len(r.tokens) for r in requests])
+    want_logprobs = any(r.params.logprobs for r in requests)
     tokens = self._decode_runner.run([r.slot for r in requests], [r.tokens[-1] for r in requests],
-                                     params, steps)
+                                     params, steps, logprobs=want_logprobs)
+    lp_rows = self._decode_runner.last_logprobs if want_logprobs else None
     finished: list[Request] = []
     for i in range(steps):
       row = tokens[i].tolist()
       live = [(j, e) for j, e in enumerate(plan.entries) if e.request.status.value == "running"]
       step_plan = StepPlan([e for _, e in live], [], [])
       sampled = {e.request.request_id: row[j] for j, e in live}
-      finished += self.scheduler.commit(step_plan, sampled)
+      logprobs = None
+      if lp_rows is not None:
+        lp = lp_rows[i].tolist()
+        logprobs = {e.request.request_id: lp[j] for j, e in live}
+      finished += self.scheduler.commit(step_plan, sampled, logprobs)
     # Requests that are still live hold exactly the tokens the burst cached.
     return finished
 
@@ -277,5 +291,6 @@ class Engine:
     requests = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
     while self.has_unfinished():
       self.step()
-    return [GenerationResult(r.request_id, r.prompt, r.output, r.finish_reason, r.num_preemptions)
+    return [GenerationResult(r.request_id, r.prompt, r.output, r.finish_reason, r.num_preemptions,
+                             list(r.logprobs) if r.params.logprobs else None)
             for r in requests]

@@ -51,6 +51,7 @@ class Request:
   status: Status = Status.WAITING
   finish_reason: str | None = None
   num_preemptions: int = 0
+  logprobs: list[float] = dataclasses.field(default_factory=list)  # of the generated tokens, if asked for
 
   @property
   def output(self) -> list[int]:
@@ -231,8 +232,10 @@ class Scheduler:
     self.waiting.appendleft(r)
 
   # ---- after the step -----------------------------------------------------------
-  def commit(self, plan: StepPlan, sampled: dict[object, int]) -> list[Request]:
-    """Records the step's progress and sampled tokens; returns requests that ended."""
+  def commit(self, plan: StepPlan, sampled: dict[object, int],
+             logprobs: dict[object, float] | None = None) -> list[Request]:
+    """Records the step's progress and sampled tokens (and their log-probabilities, where the
+    step computed them); returns requests that ended."""
     finished = []
     for e in plan.entries:
       r = e.request
@@ -243,6 +246,8 @@ class Scheduler:
         continue
       token = int(sampled[r.request_id])
       r.tokens.append(token)
+      if logprobs is not None and r.params.logprobs:
+        r.logprobs.append(float(logprobs[r.request_id]))
       stops = r.params.stop_token_ids if r.params.stop_token_ids is not None else self.eos_ids
       if token in stops:
         reason = "eos"

@@ -183,6 +183,7 @@ class CudaOps:
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
+        "sb_sample_logprobs": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_gemm_tcgen05": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
         "sb_keep_logits": [c_void, c_void, c_void, c_ll, c_void],
@@ -672,11 +673,16 @@ class CudaOps:
     return out
 
   # ---- sampling -------------------------------------------------------------
-  def sample(self, logits: torch.Tensor, temperature, top_k, top_p, seed, position) -> torch.Tensor:
-    """One token per row of float32 logits; the other arguments are host sequences."""
+  def sample(self, logits: torch.Tensor, temperature, top_k, top_p, seed, position, logprobs: bool = False):
+    """One token per row of float32 logits; the other arguments are host sequences.  With
+    `logprobs` also the float32 log-probability of each token under the distribution it was
+    drawn from (0 for greedy rows): (tokens, logprobs)."""
     params = self.pack_sample_params(temperature, top_k, top_p, seed, position)
     dev_params = torch.from_numpy(params).to(self.device, non_blocking=True)
-    return self.sample_device(logits, dev_params)
+    if not logprobs:
+      return self.sample_device(logits, dev_params)
+    lp = self._new(logits.shape[0], dtype=torch.float32)
+    return self.sample_device(logits, dev_params, logprobs_out=lp), lp
 
   @staticmethod
   def pack_sample_params(temperature, top_k, top_p, seed, position) -> np.ndarray:
@@ -692,16 +698,21 @@ class CudaOps:
     params[:, 5] = np.asarray(position, dtype=np.int32)
     return params
 
-  def sample_device(self, logits: torch.Tensor, dev_params: torch.Tensor,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
-    """Sampling with the parameter words already on the device."""
+  def sample_device(self, logits: torch.Tensor, dev_params: torch.Tensor, out: torch.Tensor | None = None,
+                    logprobs_out: torch.Tensor | None = None, step_counter: torch.Tensor | None = None) -> torch.Tensor:
+    """Sampling with the parameter words already on the device.  `logprobs_out` (float32 [R], or
+    [steps, R] indexed by the device-side `step_counter`) receives the tokens' log-probabilities."""
     r, vocab = logits.shape
     if out is None:
       out = self._new(r, dtype=torch.int32)
     slices = self.lib.sb_sample_slices(r, vocab)
     scratch = self._new(r * (2 + 2 * slices), dtype=torch.int32)
-    self._call("sb_sample", _ptr(logits.contiguous()), _ptr(dev_params), _ptr(out), r, vocab, _ptr(scratch))
+    logits = logits.contiguous()
+    self._call("sb_sample", _ptr(logits), _ptr(dev_params), _ptr(out), r, vocab, _ptr(scratch))
     self.launches += 2
+    if logprobs_out is not None:
+      self._call("sb_sample_logprobs", _ptr(logits), _ptr(dev_params), _ptr(out), _ptr(logprobs_out),
+                 _ptr(step_counter), r, vocab, _ptr(scratch))
     return out
 
   def keep_logits(self, logits: torch.Tensor, history: torch.Tensor, step_counter: torch.Tensor) -> None:

@@ -31,6 +31,8 @@ class SamplingParams:
   seed: int | None = None
   # Token ids that end the request when sampled; None means the model's eos ids.
   stop_token_ids: tuple[int, ...] | None = None
+  # Also return the log-probability of every emitted token (0 for greedy requests).
+  logprobs: bool = False
 
   def __post_init__(self):
     if self.temperature < 0:

@@ -289,6 +289,26 @@ def top_p_mask(logits, top_p):
   return mask
 
 
+def token_logprob(logits, token, temperature, top_k, top_p):
+  """simply/utils/sampling_lib.py:540-601: the log-probability of `token` under the distribution
+  `sample_token` draws from: 0 for a greedy row (the token is the argmax); otherwise the
+  log-softmax of logits / temperature over the entries that top-k and top-p keep."""
+  logits = np.asarray(logits, np.float32)
+  if temperature == 0 or top_k == 1:
+    return 0.0 if int(np.argmax(logits)) == token else float("-inf")
+  scaled = (logits / np.float32(temperature)).astype(np.float64)
+  keep = np.ones(logits.shape, bool)
+  if top_k > 0:
+    keep &= top_k_mask(scaled.astype(np.float32), top_k)
+  if top_p < 1.0:
+    inner = np.where(keep, scaled, -np.inf).astype(np.float32)
+    keep &= top_p_mask(inner, top_p)
+  if not keep[token]:
+    return float("-inf")
+  kept = scaled[keep]
+  return float(scaled[token] - kept.max() - np.log(np.exp(kept - kept.max()).sum()))
+
+
 def sample_token(logits, temperature, top_k, top_p, seed, position):
   """simply/utils/sampling_lib.py:472-537: greedy when temperature == 0 or top_k == 1;
   otherwise logits / temperature, masked by top-k and top-p (top-p within the

@@ -165,11 +165,17 @@ class ReferenceOps:
     return out.reshape(t, num_heads * head_dim).to(self.dtype)
 
   # ---- sampling -------------------------------------------------------------
-  def sample(self, logits, temperature, top_k, top_p, seed, position):
+  def sample(self, logits, temperature, top_k, top_p, seed, position, logprobs=False):
     """logits f32 [R, V]; the other arguments are host sequences of length R."""
+    rows = [logits[i].float().cpu().numpy() for i in range(logits.shape[0])]
     out = [
-        plain.sample_token(logits[i].float().cpu().numpy(), float(temperature[i]), int(top_k[i]),
-                           float(top_p[i]), int(seed[i]), int(position[i]))
+        plain.sample_token(rows[i], float(temperature[i]), int(top_k[i]), float(top_p[i]), int(seed[i]),
+                           int(position[i]))
         for i in range(logits.shape[0])
     ]
-    return torch.tensor(out, dtype=torch.int32, device=logits.device)
+    tokens = torch.tensor(out, dtype=torch.int32, device=logits.device)
+    if not logprobs:
+      return tokens
+    lp = [plain.token_logprob(rows[i], out[i], float(temperature[i]), int(top_k[i]), float(top_p[i]))
+          for i in range(logits.shape[0])]
+    return tokens, torch.tensor(lp, dtype=torch.float32, device=logits.device)

@@ -252,3 +252,17 @@ def test_a_need_with_a_rule_of_its_own_forms_a_group_of_its_own():
     m.extend([(s, 1)])
     m.check_invariants()
   assert m.groups[0].first_page[s] == (19 - 5) // 2 and m.groups[1].first_page[s] == (19 - 5) // 2 // 2 * 2
+
+
+def test_a_waiting_request_keeps_no_more_than_its_window():
+  """A request that got a long portion and then waits holds window + portion tokens; the pages
+  below its window go back as soon as another step has to take pages."""
+  m = manager(window=6, page=4, pages=12, slots=2, max_len=64)
+  a, b = m.acquire_slot("a"), m.acquire_slot("b")
+  m.extend([(a, 30)])
+  assert len(rows(m)[a]) == 8 and m.groups[0].pool.num_free == 4
+  assert m.pages_short([(b, 24)]) == 0  # 6 pages wanted, 4 free, 6 more come back from a
+  m.extend([(b, 24)])
+  assert m.groups[0].first_page[a] == (30 - 5) // 4 and len(rows(m)[a]) == 2
+  assert len(rows(m)[b]) == 6
+  m.check_invariants()

@@ -10,6 +10,7 @@ from simply_b200 import Engine, EngineConfig, SamplingParams, StepEntry
 from simply_b200.engine.replay import engine_for_replay
 from tests import replay_cases as cases
 from tests import trace_util
+from tests.plain import gemma2_plain as plain_lib
 from tests.plain.gemma2_plain import PlainGemma2
 from tests.reference_ops import ReferenceOps
 from tests.tiny_models import write_tiny
@@ -75,6 +76,33 @@ def test_generation_equals_plain(models, which, lengths, steps, page):
   got = eng.generate(prompts, SamplingParams(temperature=0.8, seed=3, max_decode_steps=steps, stop_token_ids=()))
   assert [r.output_token_ids for r in got] == [plain.sample(p, steps, 0.8, 3) for p in prompts]
   eng.cache.check_invariants()
+
+
+def test_logprobs_and_default_seeds(models):
+  """simply/utils/sampling_lib.py:540-601: every output token comes with its log-probability under
+  the distribution it was drawn from (0 for greedy requests).  Requests without a seed each get
+  one of their own, so equal prompts draw different samples; an explicit seed repeats itself."""
+  folder, plain, _, _ = models["b"]
+  rng = np.random.default_rng(6)
+  prompts = [rng.integers(0, plain.cfg["vocab_size"], n).tolist() for n in (12, 31)]
+  eng = cpu_engine(folder, page_size=8, max_num_issue_tokens=16)
+  sp = SamplingParams(temperature=0.7, top_k=30, top_p=0.9, seed=5, max_decode_steps=6, stop_token_ids=(),
+                      logprobs=True)
+  for p, r in zip(prompts, eng.generate(prompts, sp)):
+    assert r.output_token_ids == plain.sample(p, 6, 0.7, 5, top_k=30, top_p=0.9)
+    logits = plain.forward(p + r.output_token_ids)
+    want = [plain_lib.token_logprob(logits[len(p) - 1 + i], t, 0.7, 30, 0.9) for i, t in enumerate(r.output_token_ids)]
+    np.testing.assert_allclose(r.output_token_logprobs, want, atol=2e-4)
+    assert all(v <= 0 for v in r.output_token_logprobs)
+  greedy = eng.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=4, stop_token_ids=(), logprobs=True))
+  assert all(r.output_token_logprobs == [0.0] * 4 for r in greedy)
+  assert eng.generate(prompts[:1], SamplingParams(max_decode_steps=2))[0].output_token_logprobs is None
+  # no seed: the same prompt twice draws two different continuations; with a seed, the same one
+  same = [prompts[0], prompts[0]]
+  a, b = eng.generate(same, SamplingParams(temperature=1.0, max_decode_steps=12, stop_token_ids=()))
+  assert a.output_token_ids != b.output_token_ids
+  a, b = eng.generate(same, SamplingParams(temperature=1.0, seed=9, max_decode_steps=12, stop_token_ids=()))
+  assert a.output_token_ids == b.output_token_ids == plain.sample(prompts[0], 12, 1.0, 9)
 
 
 def test_eos_ends_a_request(models):

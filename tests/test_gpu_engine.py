@@ -161,6 +161,49 @@ def test_random_workloads_float32_equal_plain(folders, seed):
   assert eng.cache.all_pages_free()
 
 
+def test_logprobs_from_eager_steps_and_from_graph_bursts(folders):
+  """Every output token's log-probability under the distribution it was drawn from, from prompt
+  steps (eager) and decode bursts (CUDA graphs) alike, against the plain statement."""
+  from tests.plain import gemma2_plain as plain_lib
+  plain = PlainGemma2(folders["b"])
+  prompts = prompts_for(plain, (7, 26, 51), seed=31)
+  sp = [SamplingParams(temperature=0.8, top_k=k, top_p=p, seed=60 + i, max_decode_steps=14, stop_token_ids=(),
+                       logprobs=i != 1)
+        for i, (k, p) in enumerate(((-1, 1.0), (25, 1.0), (40, 0.85)))]
+  eng = engine_for(folders["b"], "float32", intermediate_steps=4)
+  results = eng.generate(prompts, sp)
+  eng.ops.check_errors()
+  assert results[1].output_token_logprobs is None
+  for i in (0, 2):
+    p, r = prompts[i], results[i]
+    assert r.output_token_ids == plain.sample(p, 14, 0.8, 60 + i, top_k=sp[i].top_k, top_p=sp[i].top_p)
+    logits = plain.forward(p + r.output_token_ids)
+    want = [plain_lib.token_logprob(logits[len(p) - 1 + j], t, 0.8, sp[i].top_k, sp[i].top_p)
+            for j, t in enumerate(r.output_token_ids)]
+    np.testing.assert_allclose(r.output_token_logprobs, want, atol=3e-4)
+
+
+def test_a_float32_folder_served_in_bfloat16(tmp_path):
+  """Matrices stored in 32 bits are narrowed to the activation dtype on load
+  (simply/utils/checkpoint_lib.py:658-670): the engine holds bfloat16 matrices, runs the bfloat16
+  kernels and gives the logits of the bfloat16 folder."""
+  wide = write_tiny("b", tmp_path / "wide", "float32")
+  narrow = write_tiny("b", tmp_path / "narrow", "bfloat16")
+  plain = PlainGemma2(narrow)
+  toks = prompts_for(plain, (45,), seed=17)[0]
+  rows = {}
+  for name, folder in (("wide", wide), ("narrow", narrow)):
+    eng = engine_for(folder, "bfloat16")
+    assert eng.model.blocks["model.layers.0"].mixer.qkv_weight.dtype == torch.bfloat16
+    assert eng.model.embedding.table.dtype == torch.bfloat16
+    slot = eng.open_request()
+    rows[name] = eng.step_raw([StepEntry(slot, toks, tuple(range(len(toks))))]).cpu().numpy()
+  assert_logits_close(rows["wide"], plain.forward(toks), "bfloat16", "float32 folder")
+  assert np.abs(rows["wide"] - rows["narrow"]).max() <= 0.01 * np.abs(rows["narrow"]).max()
+  kept = engine_for(wide, "bfloat16", keep_float32_weights=True)
+  assert kept.model.blocks["model.layers.0"].mixer.qkv_weight.dtype == torch.float32
+
+
 def test_engine_refuses_without_cuda_kernels(monkeypatch):
   from simply_b200.kernels import ops as ops_mod
   monkeypatch.setattr(torch.cuda, "is_available", lambda: False)

@@ -514,6 +514,13 @@ def test_sample_matches_plain_statement(table, vocab):
   want = [plain.sample_token(logits[i].numpy(), temperature[i], top_k[i], top_p[i], seed[i], position[i])
           for i in range(rows)]
   assert got == want
+  # the same draw with the tokens' log-probabilities (simply/utils/sampling_lib.py:540-601)
+  temperature[3], top_k[6] = 0.0, 1  # two greedy rows: log-probability 0
+  tokens, logprobs = ops.sample(logits.cuda(), temperature, top_k, top_p, seed, position, logprobs=True)
+  want_lp = [plain.token_logprob(logits[i].numpy(), int(tokens[i]), temperature[i], top_k[i], top_p[i])
+             for i in range(rows)]
+  np.testing.assert_allclose(logprobs.cpu().numpy(), want_lp, atol=1e-4)
+  assert logprobs[3] == 0 and logprobs[6] == 0 and (logprobs <= 0).all()
 
 
 def test_sample_is_distributed_as_softmax(table):

@@ -4,7 +4,7 @@
     EMBEDDINGS, and an output layer of its own kind (a matrix of its own, not the embedding
     table), registered in HEADS;
   * a feed-forward with routing that keeps to device tensors (every expert runs on every token,
-    the router's choice selects), and therefore says `graph_safe = True`;
+    weighted by the router's softmax), and therefore says `graph_safe = True`;
   * two attention layers with the same window and the same group but different head sizes and
     numbers of kv heads (work lists cut for one must not serve the other);
 
@@ -72,8 +72,9 @@ class UntiedHead(Head):
 
 
 class DenselyRoutedFeedForward(FeedForward):
-  """Top-1 routing without a look at the host: every expert acts on every token and the router's
-  choice (float32 logits) selects one result, weighted by the router's softmax."""
+  """Soft routing without a look at the host: every expert acts on every token and the results
+  are mixed with the router's softmax (float32 logits).  (The top-1 routing of the neighbouring
+  test file jumps when bfloat16 rounding turns a near-tie of the router; a mixture does not.)"""
 
   graph_safe = True
 
@@ -96,11 +97,10 @@ class DenselyRoutedFeedForward(FeedForward):
     ops = ctx.ops
     logits = x.float() @ self.router.t()
     prob = torch.softmax(logits, dim=-1)
-    choice = torch.argmax(logits, dim=-1)
     out = torch.zeros_like(x, dtype=torch.float32)
     for e in range(self.experts):
       y = ops.linear(ops.gated_linear(x, self.gate_up[e], 0), self.down[e]).float()
-      out = torch.where((choice == e)[:, None], y * prob[:, e:e + 1], out)
+      out = out + y * prob[:, e:e + 1]
     return out.to(x.dtype)
 
 
@@ -156,10 +156,10 @@ def plain_forward(t, tokens):
     prob = np.exp(logits - logits.max(-1, keepdims=True))
     prob /= prob.sum(-1, keepdims=True)
     out = np.zeros_like(y)
-    for i, e in enumerate(np.argmax(logits, -1)):
+    for e in range(EXPERTS):
       gu = f(f"{name}.moe.experts.{e}.gate_up.weight")
-      z = plain.gated_feed_forward(y[i:i + 1], gu[:HIDDEN], gu[HIDDEN:], f(f"{name}.moe.experts.{e}.down.weight"))
-      out[i] = z[0] * prob[i, e]
+      z = plain.gated_feed_forward(y, gu[:HIDDEN], gu[HIDDEN:], f(f"{name}.moe.experts.{e}.down.weight"))
+      out += z * prob[:, e:e + 1]
     h = h + out
   return plain.rms_norm(h, f("final.weight"), EPS) @ f("out.weight").T
 

@@ -50,9 +50,15 @@ def test_static_scratch_sampling_matches_the_ordinary_entry_point():
   ops = CudaOps(torch.float32)
   fn = load_symbol()
   stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-  # Two calls in a row; the second has fewer rows and another vocabulary, so stale words of
-  # the first call lie right next to the ones it uses.
-  for rows, vocab, seed in ((37, 25601, 0), (5, 1003, 1), (MAX_ROWS, 300, 2)):
+  # Calls in a row; a call with fewer rows or another vocabulary finds stale words of the one
+  # before right next to the ones it uses.  (4, 70001) and (3, 256000) cut a row into the most
+  # slices the array is laid out for (64: few rows, a vocabulary of at least 65,536), each after a
+  # larger call; (MAX_ROWS, 300) uses the most rows.
+  cases = ((37, 25601, 0), (5, 1003, 1), (MAX_ROWS, 300, 2), (4, 70001, 3), (MAX_ROWS, 2100, 4), (3, 256000, 5),
+           (9, 65536, 6))
+  for rows, vocab, seed in cases:
+    if rows <= 9 and vocab >= 65536:
+      assert ops.lib.sb_sample_slices(rows, vocab) == 64
     logits, params = make_case(ops, rows, vocab, seed)
     want = ops.sample_device(logits, params)
     out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
