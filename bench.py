@@ -462,32 +462,38 @@ def main(argv=None):
   value = args.batch / (ms_step * 1e-3)
 
   # ---- end to end through the public entry point (next, while the GPU is in the same state) ---
+  # The prompts are computed under the engine's own token budget, in steps that also decode for
+  # the requests whose prompts are done; the requests therefore begin to decode a few steps apart
+  # and are a few tokens apart in the timed steps (`slack`), all of them just below the full context.
   rng = np.random.default_rng(4)
-  start = context - args.steps - args.warmup
+  slack = -(-context // ec.max_num_issue_tokens) * args.batch + 8
+  start = context - args.steps - args.warmup - slack
   prompts = [rng.integers(0, cfg.vocab_size, start).tolist() for _ in range(args.batch)]
-  sp = SamplingParams(temperature=0.0, max_decode_steps=args.steps + args.warmup, stop_token_ids=())
+  sp = SamplingParams(temperature=0.0, max_decode_steps=args.steps + args.warmup + slack, stop_token_ids=())
   requests = [engine.add_request(p, sp) for p in prompts]
-  # All prompts in one step, so that every request starts to decode at the same step.
-  engine.scheduler.max_num_issue_tokens = args.batch * context
   while any(not r.is_decoding for r in requests):
-    engine.step()  # prompt portions (untimed)
+    engine.step()  # prompt portions beside decoded tokens (untimed)
   settle(torch)
-  for _ in range(args.warmup - 1):
+  for _ in range(args.warmup):
     engine.step()
   torch.cuda.synchronize()
   runner = engine._decode_runner
   h2d0, d2h0 = runner.h2d_bytes, runner.d2h_bytes
   t0 = time.perf_counter()
   e2e_steps = 0
-  while engine.has_unfinished() and e2e_steps < args.steps:
+  step_ends = []
+  while e2e_steps < args.steps:
     engine.step()
     e2e_steps += 1
+    step_ends.append(time.perf_counter())
   torch.cuda.synchronize()
   e2e_s = time.perf_counter() - t0
+  assert all(r.is_decoding for r in requests), "a request ended inside the timed steps"
+  step_ms = np.diff(np.array([t0] + step_ends)) * 1e3
   h2d = (runner.h2d_bytes - h2d0) // max(e2e_steps, 1)  # counted where the copies are made
   d2h = (runner.d2h_bytes - d2h0) // max(e2e_steps, 1)
-  while engine.has_unfinished():
-    engine.step()
+  for r in requests:
+    engine.cancel(r.request_id)
   e2e_value = args.batch * e2e_steps / e2e_s
 
   points = {}
@@ -565,7 +571,8 @@ def main(argv=None):
       },
       "bursts_ms_per_step": [round(b, 4) for b in bursts_ms],
       "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-              "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+              "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+              "median_step_ms": round(float(np.median(step_ms)), 4), "max_step_ms": round(float(step_ms.max()), 4)},
       "gpu_launches": int(round(launches * args.steps)),
       "prefill": prefill,
       "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",

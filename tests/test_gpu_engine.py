@@ -199,7 +199,8 @@ def test_a_float32_folder_served_in_bfloat16(tmp_path):
     slot = eng.open_request()
     rows[name] = eng.step_raw([StepEntry(slot, toks, tuple(range(len(toks))))]).cpu().numpy()
   assert_logits_close(rows["wide"], plain.forward(toks), "bfloat16", "float32 folder")
-  assert np.abs(rows["wide"] - rows["narrow"]).max() <= 0.01 * np.abs(rows["narrow"]).max()
+  # (not bit-equal: the norm scales of the float32 folder stay in 32 bits, the other folder's are rounded)
+  assert_logits_close(rows["wide"], rows["narrow"], "bfloat16", "float32 folder against bfloat16 folder")
   kept = engine_for(wide, "bfloat16", keep_float32_weights=True)
   assert kept.model.blocks["model.layers.0"].mixer.qkv_weight.dtype == torch.float32
 
