@@ -67,7 +67,7 @@ class PageGroup:
   def plan(self, slot: int, cur_len: int, n_new: int) -> tuple[int, int]:
     """(pages to give back, pages to take) for `n_new` tokens after `cur_len` cached ones."""
     first, end = int(self.first_page[slot]), int(self.end_page[slot])
-    new_first = max(first, int(self.need.first_needed_page(np.array([cur_len]), self.page_size)[0]))
+    new_first = max(first, self.need.first_needed_page_of(cur_len, self.page_size))
     new_first = min(new_first, end)
     new_end = max(end, _cdiv(cur_len + n_new, self.page_size))
     return new_first - first, new_end - end
@@ -267,13 +267,16 @@ class CacheManager:
       return 0
     short = 0
     busy = {slot for slot, _ in entries}
+    slots = np.fromiter((s for s, _ in entries), dtype=np.int64, count=len(entries))
+    new = np.fromiter((n for _, n in entries), dtype=np.int64, count=len(entries))
+    cur = self.lengths[slots]
     for g in self.groups:
-      take = 0
-      back = sum(n for _, n in self._idle_releasable(g, busy))
-      for slot, n in entries:
-        b, t = g.plan(slot, int(self.lengths[slot]), n)
-        back += b
-        take += t
+      # `PageGroup.plan` for all entries at once.
+      first, end = g.first_page[slots], g.end_page[slots]
+      new_first = np.minimum(np.maximum(first, g.need.first_needed_page(cur, self.page_size)), end)
+      new_end = np.maximum(end, -(-(cur + new) // self.page_size))
+      back = int((new_first - first).sum()) + sum(n for _, n in self._idle_releasable(g, busy))
+      take = int((new_end - end).sum())
       short = max(short, take - back - g.pool.num_free)
     return max(short, 0)
 

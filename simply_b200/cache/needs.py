@@ -48,6 +48,12 @@ class PagedKVNeed:
       return np.zeros_like(lengths)
     return np.maximum(lengths - (self.window - 1), 0) // page_size
 
+  def first_needed_page_of(self, length: int, page_size: int) -> int:
+    """`first_needed_page` for one request, in plain integers (the books' inner loops use it)."""
+    if type(self).first_needed_page is PagedKVNeed.first_needed_page:
+      return 0 if self.window is None else max(length - (self.window - 1), 0) // page_size
+    return int(self.first_needed_page(np.array([length], dtype=np.int64), page_size)[0])
+
   def pool_pages(self, *, page_size: int, max_slots: int, max_seq_len: int, all_pages: int,
                  step_tokens: int, burst_tokens: int) -> int:
     """Pages the group's pool needs so that it never runs out before a pool that keeps every
