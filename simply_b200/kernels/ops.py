@@ -16,6 +16,7 @@ norms, rotation, cache write, activation, embedding, sampling) is hand-written.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any, Sequence
 
 import numpy as np
@@ -115,8 +116,10 @@ class AttentionGraphPlan:
 class CudaOps:
 
   name = "cuda"
-  # Largest token count the weight-streaming product takes.
+  # Largest token count the weight-streaming product for a handful of tokens takes, and the largest
+  # the one for a serving batch takes (csrc/gemm_skinny_bf16.cu, csrc/gemm_stream_tc.cu).
   skinny_max_rows = 16
+  mid_max_rows = 128
 
   def __init__(self, dtype: torch.dtype = torch.bfloat16, device: str | torch.device = "cuda"):
     if dtype not in (torch.float32, torch.bfloat16):
@@ -156,6 +159,22 @@ class CudaOps:
     self.skinny_warps = 0
     # False keeps the q, k, v projection and the rotation + cache write as two kernels (tests).
     self.fused_qkv_rope = True
+    # False sends steps of 17 to 64 tokens to the library product (tests, experiments); mid_split
+    # fixes the number of blocks that share a row tile's k (0: the launch chooses).
+    self.mid_rows_kernel = True
+    # Most rows for which each kind of product takes that kernel rather than the library's: the
+    # fused q, k, v projection, the gated product, a plain product, the output layer.  The kernel
+    # takes up to 128 rows; measured inside decode steps of the Gemma 2 2B shape it is ahead of
+    # the library's products up to 32 rows (by 1 to 2 % of the step) and behind them from 33
+    # (by 1 to 4 %), so that is where the line is drawn.
+    self.mid_rows = {"qkv": 32, "gated": 32, "plain": 32, "head": 32}
+    env = os.environ.get("SIMPLY_B200_SERVING_BATCH_PRODUCT")  # experiments: "qkv:128,gated:32,plain:0,head:128"
+    if env:
+      for item in env.split(","):
+        name, _, rows = item.partition(":")
+        self.mid_rows[name] = int(rows or 128)
+    self.mid_split = 0
+    self.mid_stages = 0  # 0 or 8: the deep ring of stages, 4: the shallow one (experiments)
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
@@ -178,13 +197,16 @@ class CudaOps:
         "sb_soft_cap": [c_void, c_float, c_ll, c_void],
         "sb_gemm_f32_nt": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_void],
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
+        "sb_gemm_stream_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                              c_void, c_void],
+        "sb_qkv_rope_stream_tc": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
+                                  c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_int, c_int, c_void],
         "sb_qkv_rope_skinny": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
                                c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_int, c_void],
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_sample_logprobs": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void],
-        "sb_gemm_tcgen05": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
         "sb_keep_logits": [c_void, c_void, c_void, c_ll, c_void],
     }
@@ -462,6 +484,16 @@ class CudaOps:
     self._call("sb_cast", _ptr(x), _code(x), _ptr(out), _code(out), x.numel())
     return out
 
+  def _mid_product(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, cap: float = 0.0,
+                   activation: int = 0, split: int | None = None) -> bool:
+    """The weight-streaming product for a serving batch (17 to 128 tokens); False when it does
+    not take the shape."""
+    m, k = x.shape
+    n = w.shape[0]
+    split = self.mid_split if split is None else split
+    return self._call("sb_gemm_stream_tc", _ptr(x), _ptr(w), _ptr(out), m, n, k, epilogue, float(cap), activation,
+                      split, self.mid_stages, _ptr(self.err)) == 0
+
   def linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """x [M, K] . w[N, K]^T -> [M, N] in the activation dtype."""
     m, k = x.shape
@@ -477,22 +509,15 @@ class CudaOps:
       out = self._new(m, n, dtype=torch.bfloat16)
       if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w), _ptr(out), m, n, k, 0, 0.0, 0, self.skinny_warps) == 0:
         return out
+    elif m <= self.mid_rows["plain"] and self.mid_rows_kernel and x.is_contiguous() and w.is_contiguous():
+      out = self._new(m, n, dtype=torch.bfloat16)
+      if self._mid_product(x, w, out, 0):
+        return out
     if self.direct_library_products and x.is_contiguous() and w.is_contiguous():
       out = self._new(m, n, dtype=torch.bfloat16)
       if self._library_product(x, w, out):
         return out
     return torch.mm(x, w.t())
-
-  def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, *, out_f32: bool = False, cap: float = 0.0,
-                     tile_n: int = 128) -> torch.Tensor | None:
-    """x [M, K] . w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate in tensor
-    memory); None when the shape is not taken (K not a multiple of 8)."""
-    m, k = x.shape
-    n = w.shape[0]
-    out = self._new(m, n, dtype=torch.float32 if out_f32 else torch.bfloat16)
-    rc = self._call("sb_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(out), m, n, k, int(out_f32), float(cap), tile_n,
-                    _ptr(self.err))
-    return out if rc == 0 else None
 
   def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, activation: int) -> torch.Tensor:
     """act(x . w_gate^T) * (x . w_up^T) with w_gate_up = [gate rows; up rows]: [M, N/2]."""
@@ -502,6 +527,11 @@ class CudaOps:
       out = self._new(m, n // 2, dtype=torch.bfloat16)
       if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n, k, 2, 0.0,
                     activation, self.skinny_warps) == 0:
+        return out
+    if (w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.mid_rows_kernel
+        and self.skinny_max_rows < m <= self.mid_rows["gated"] and x.is_contiguous() and w_gate_up.is_contiguous()):
+      out = self._new(m, n // 2, dtype=torch.bfloat16)
+      if self._mid_product(x, w_gate_up, out, 2, activation=activation):
         return out
     return self.gated_activation(self.linear(x, w_gate_up), activation)
 
@@ -516,6 +546,10 @@ class CudaOps:
       return out
     x = self.cast(x, torch.bfloat16)
     chunk = 32
+    if chunk < r <= self.mid_rows["head"] and self.mid_rows_kernel and k % 8 == 0 and x.is_contiguous():
+      # 33 to 128 rows: one pass over the table instead of several
+      if self._mid_product(x, table, out, 1, cap=cap, split=1):
+        return out
     if r > chunk and k % 8 == 0:
       if self.direct_library_products and x.is_contiguous() and self._library_product(x, table, out):
         self._call("sb_soft_cap", _ptr(out), float(cap), out.numel())
@@ -620,6 +654,20 @@ class CudaOps:
                       _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
                       _ptr(ctx.positions), num_heads, num_kv_heads, head_dim, ctx.page_size,
                       storage.shape[0] if storage is not None else 0, _ptr(self.err), self.skinny_warps)
+      if rc == 0:
+        return q
+    if (self.fused_qkv_rope and self.mid_rows_kernel and self.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+        and self.skinny_max_rows < t <= self.mid_rows["qkv"] and head_dim % 128 == 0 and k % 8 == 0):
+      x = self.cast(x, torch.bfloat16)
+      q = self._new(t, num_heads, head_dim, dtype=torch.bfloat16)
+      cos, sin = tables if tables is not None else (None, None)
+      if storage is not None and storage.dtype != torch.bfloat16:
+        raise KernelError("cache and activations must share one dtype")
+      args = (_ptr(x), _ptr(w_qkv), t, k, _ptr(cos), _ptr(sin), float(q_scale),
+              _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
+              _ptr(ctx.positions), num_heads, num_kv_heads, head_dim, ctx.page_size,
+              storage.shape[0] if storage is not None else 0, _ptr(self.err), self.mid_split)
+      rc = self._call("sb_qkv_rope_stream_tc", *args, self.mid_stages)
       if rc == 0:
         return q
     qkv = self.linear(x, w_qkv)

@@ -211,8 +211,8 @@ def test_linear_float32_is_true_float32(table, m, n, k):
   assert torch.equal(alone[0], got[m // 2])
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 200])
-@pytest.mark.parametrize("n,k", [(48, 64), (1000, 96), (2304, 2048), (100, 328)])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 24, 32, 33, 47, 64, 65, 200])
+@pytest.mark.parametrize("n,k", [(48, 64), (1000, 96), (2304, 2048), (100, 328), (130, 9216), (4096, 2304)])
 def test_linear_bfloat16(table, m, n, k):
   ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
   x = torch.randn(m, k).to(torch.bfloat16)
@@ -220,7 +220,80 @@ def test_linear_bfloat16(table, m, n, k):
   close(ops.linear(x.cuda(), w.cuda()), ref.linear(x, w), torch.bfloat16)
 
 
-@pytest.mark.parametrize("m", [33, 64, 65, 100, 700, 2048])
+@pytest.mark.parametrize("stages", [0, 8])
+@pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("m,n,k", [(17, 128, 128), (33, 300, 1032), (64, 2304, 2048), (50, 257, 2304), (64, 129, 8),
+                                   (100, 1000, 2304), (128, 2304, 9216)])
+def test_serving_batch_product_with_k_split_over_a_cluster(table, stages, split, m, n, k):
+  """The product for 17 to 128 tokens, with the sum over k in one block or split over the blocks of
+  a cluster (their partial sums are added in rank order: the same result every time)."""
+  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
+  x = torch.randn(m, k).to(torch.bfloat16).cuda()
+  w = (torch.randn(n, k) / k ** 0.5).to(torch.bfloat16).cuda()
+  ops.mid_split, ops.mid_stages = split, stages
+  kept, ops.mid_rows = ops.mid_rows, dict.fromkeys(ops.mid_rows, 128)  # whatever the engine's own limit is
+  try:
+    before = ops.launches
+    got = ops.linear(x, w)
+    assert ops.launches == before + 1
+    again = ops.linear(x, w)
+  finally:
+    ops.mid_split, ops.mid_stages, ops.mid_rows = 0, 0, kept
+  ops.check_errors()
+  close(got, ref.linear(x.cpu(), w.cpu()), torch.bfloat16)
+  assert torch.equal(got, again)
+  ops.mid_rows_kernel = False
+  try:
+    close(got, ops.linear(x, w), torch.bfloat16)  # the library product of the same shape
+  finally:
+    ops.mid_rows_kernel = True
+
+
+@pytest.mark.parametrize("hq,hkv,dh,ps,width", [(3, 1, 128, 16, 200), (8, 4, 256, 64, 2304), (2, 2, 128, 8, 72)])
+@pytest.mark.parametrize("seqs", [[(0, 17)], [(37, 1)] * 20 + [(130, 6), (5, 30)], [(200, 1)] * 64, [(0, 40), (90, 24)],
+                                  [(3, 1)] * 90 + [(70, 38)]],
+                         ids=["prompt17", "mixed56", "decode64", "two64", "mixed128"])
+def test_project_rotate_store_fused_for_a_serving_batch(table, hq, hkv, dh, ps, width, seqs):
+  """Steps of 17 to 128 tokens: projection, rotation, query scale and cache write in one kernel,
+  against the two-kernel path and the plain statement."""
+  dtype = torch.bfloat16
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  kept, ops.mid_rows = ops.mid_rows, dict.fromkeys(ops.mid_rows, 128)
+  try:
+    _check_fused_serving_batch(ops, ref, dtype, hq, hkv, dh, ps, width, seqs)
+  finally:
+    ops.mid_rows = kept
+
+
+def _check_fused_serving_batch(ops, ref, dtype, hq, hkv, dh, ps, width, seqs):
+  sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=None, page_size=ps, dtype=dtype,
+                     device="cuda", ops=ops, seed=6)
+  t = sc.ctx.num_tokens
+  assert 16 < t <= 128
+  x = torch.randn(t, width).to(dtype).cuda()
+  w = (torch.randn((hq + 2 * hkv) * dh, width) / width ** 0.5).to(dtype).cuda()
+  rot = ops.rotation_tables(sc.ctx.positions, torch.linspace(1, 900, dh // 2).cuda(), 1.0)
+  st_ref, st_two = sc.storage.clone(), sc.storage.clone()
+  q_ref = ref.project_rotate_store(x, w, rot, 0.37, hq, hkv, dh, st_ref, sc.block_table, sc.ctx)
+  before = ops.launches
+  q = ops.project_rotate_store(x, w, rot, 0.37, hq, hkv, dh, sc.storage, sc.block_table, sc.ctx)
+  assert ops.launches - before == 1  # one kernel
+  ops.check_errors()
+  ops.fused_qkv_rope = False
+  try:
+    q_two = ops.project_rotate_store(x, w, rot, 0.37, hq, hkv, dh, st_two, sc.block_table, sc.ctx)
+  finally:
+    ops.fused_qkv_rope = True
+  close(q, q_ref, dtype, 3.0)
+  close(q, q_two, dtype, 3.0)
+  torch.testing.assert_close(sc.storage.float().cpu(), st_ref.float().cpu(), equal_nan=True, **tol(dtype, 3.0))
+  torch.testing.assert_close(sc.storage.float().cpu(), st_two.float().cpu(), equal_nan=True, **tol(dtype, 3.0))
+  wq = w[:hq * dh].contiguous()
+  q_plain = ops.project_rotate_store(x, wq, None, 1.0, hq, 0, dh, None, sc.block_table, sc.ctx)
+  close(q_plain.reshape(t, -1), ref.linear(x, wq), dtype, 3.0)
+
+
+@pytest.mark.parametrize("m", [33, 64, 100, 700, 2048])
 def test_library_product_is_called_directly(table, m):
   """Steps of more than 32 tokens: the library product, called by the package's own code with an
   algorithm kept per size class (one launch counted, no tensor-library call), gives what the
@@ -242,30 +315,23 @@ def test_library_product_is_called_directly(table, m):
   close(got, through_torch.cpu(), torch.bfloat16)
 
 
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 64, 128), (200, 1000, 2304), (2048, 2304, 2048), (64, 4096, 328),
-                                   (5, 70, 72)])
-def test_linear_tcgen05(table, tile_n, m, n, k):
-  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
-  x = torch.randn(m, k).to(torch.bfloat16)
-  w = (torch.randn(n, k) / k ** 0.5).to(torch.bfloat16)
-  got = ops.linear_tcgen05(x.cuda(), w.cuda(), tile_n=tile_n)
-  ops.check_errors()
-  close(got, ref.linear(x, w), torch.bfloat16)
-  got = ops.linear_tcgen05(x.cuda(), w.cuda(), out_f32=True, cap=3.0, tile_n=tile_n)
-  ops.check_errors()
-  torch.testing.assert_close(got.cpu(), ref.lm_head(x, w, 3.0), atol=2e-3, rtol=1e-3)
-
-
-@pytest.mark.parametrize("m", [1, 8, 13, 40])
-@pytest.mark.parametrize("f,k,act", [(160, 96, 0), (1000, 64, 1), (9216 // 4, 2304, 0)])
+@pytest.mark.parametrize("m", [1, 8, 13, 17, 40, 64, 70, 128, 130])
+@pytest.mark.parametrize("f,k,act", [(160, 96, 0), (1000, 64, 1), (9216 // 4, 2304, 0), (100, 2048, 2)])
 def test_gated_linear(table, m, f, k, act):
   torch.manual_seed(1000 * m + f)
-  for dtype in DTYPES:
+  for dtype, own_up_to in ((torch.float32, None), (torch.bfloat16, None), (torch.bfloat16, 128)):
+    # (own_up_to = 128: the engine's own product with the activation in its epilogue for every
+    # row count it takes, not only for those where it is faster than the library's)
     ops, ref = table[dtype], ReferenceOps(dtype)
     x = torch.randn(m, k).to(dtype)
     w = (torch.randn(2 * f, k) / k ** 0.5 * 2).to(dtype)
-    got, want = ops.gated_linear(x.cuda(), w.cuda(), act), ref.gated_linear(x, w, act)
+    kept = ops.mid_rows
+    if own_up_to:
+      ops.mid_rows = dict.fromkeys(kept, own_up_to)
+    try:
+      got, want = ops.gated_linear(x.cuda(), w.cuda(), act), ref.gated_linear(x, w, act)
+    finally:
+      ops.mid_rows = kept
     if dtype == torch.float32:
       close(got, want, dtype, 2.0)
     else:
@@ -278,7 +344,8 @@ def test_gated_linear(table, m, f, k, act):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("r,v,k,cap", [(1, 1000, 96, 10.0), (7, 256, 64, 30.0), (45, 1003, 72, 0.0), (3, 25600, 2304, 30.0),
-                                       (40, 2048, 72, 30.0)])
+                                       (40, 2048, 72, 30.0), (64, 25601, 2304, 30.0), (33, 130, 1000, 0.0), (100, 5000, 96, 30.0),
+                                       (140, 1000, 96, 30.0)])
 def test_lm_head(table, dtype, r, v, k, cap):
   ops, ref = table[dtype], ReferenceOps(dtype)
   x = (torch.randn(r, k) * 2).to(dtype)
@@ -287,6 +354,14 @@ def test_lm_head(table, dtype, r, v, k, cap):
   assert got.dtype == torch.float32
   # The product is accumulated and capped in float32 in both dtypes.
   torch.testing.assert_close(got.cpu(), ref.lm_head(x, t, cap), atol=2e-4 * k ** 0.5, rtol=1e-4)
+  if dtype == torch.bfloat16 and 32 < r <= 128:
+    # the engine's own product with the soft cap in its epilogue, where the library's is the default
+    kept, ops.mid_rows = ops.mid_rows, dict.fromkeys(ops.mid_rows, 128)
+    try:
+      own = ops.lm_head(x.cuda(), t.cuda(), cap)
+    finally:
+      ops.mid_rows = kept
+    torch.testing.assert_close(own.cpu(), ref.lm_head(x, t, cap), atol=2e-4 * k ** 0.5, rtol=1e-4)
 
 
 def test_weight_stored_in_32_bits_is_used_in_32_bits(table):
