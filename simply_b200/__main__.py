@@ -50,6 +50,10 @@ flags.DEFINE_bool("use_cuda_graphs", True, "Replay decode steps from CUDA graphs
 flags.DEFINE_bool("logprobs", False, "Also print the log-probability of every output token.")
 flags.DEFINE_string("prompt_ids", None, "Prompts as token ids: '1,2,3;4,5' (';' separates prompts).")
 flags.DEFINE_string("prompt_file", None, "File with one prompt per line: token ids separated by spaces or commas.")
+flags.DEFINE_string("prompt", None, "Prompts as text ('||' separates prompts); needs a vocabulary: --vocab_path, or "
+                    "tokenizer.json / tokenizer.model in --ckpt_dir.")
+flags.DEFINE_string("vocab_path", None, "Folder with tokenizer.json (and tokenizer_config.json), or a SentencePiece "
+                    "model file (simply/serving/common_flags.py names vocabularies by --vocab_name).")
 
 
 def _parse_ids(text: str) -> list[int]:
@@ -93,8 +97,8 @@ def main(argv):
     print(json.dumps({"wrote": out}))
     return 0
   prompts = _prompts()
-  if not prompts:
-    raise app.UsageError("give --prompt_ids or --prompt_file")
+  if not prompts and not FLAGS.prompt:
+    raise app.UsageError("give --prompt_ids, --prompt_file or --prompt")
 
   from simply_b200 import Engine, SamplingParams
 
@@ -110,6 +114,21 @@ def main(argv):
                                 matrix_std=FLAGS.matrix_std, scale_std=FLAGS.scale_std)
   else:
     raise app.UsageError("give --ckpt_dir, or --experiment_config with --random_weights")
+  if FLAGS.prompt:
+    from simply_b200.text import SentencePieceVocab, TextProcessor, load_vocab
+    where = FLAGS.vocab_path or FLAGS.ckpt_dir
+    if not where:
+      raise app.UsageError("--prompt needs --vocab_path (or a model folder that holds a tokenizer)")
+    vocab = SentencePieceVocab(where) if os.path.isfile(where) else load_vocab(where)
+    processor = TextProcessor(vocab)
+    texts = [t for t in FLAGS.prompt.split("||") if t.strip()]
+    sp = SamplingParams(temperature=FLAGS.temperature, top_k=FLAGS.top_k, top_p=FLAGS.top_p,
+                        max_decode_steps=FLAGS.max_decode_steps, seed=FLAGS.seed, logprobs=FLAGS.logprobs)
+    for text, (answer, r) in zip(texts, engine.generate_text(texts, sp, processor=processor)):
+      print(json.dumps({"request_id": r.request_id, "prompt": text, "text": answer,
+                        "output_token_ids": r.output_token_ids, "finish_reason": r.finish_reason}))
+    if not prompts:
+      return 0
   params = [SamplingParams(temperature=FLAGS.temperature, top_k=FLAGS.top_k, top_p=FLAGS.top_p,
                            max_decode_steps=FLAGS.max_decode_steps, seed=FLAGS.seed + i, logprobs=FLAGS.logprobs)
             for i in range(len(prompts))]

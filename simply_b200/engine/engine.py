@@ -280,6 +280,25 @@ class Engine:
     # Requests that are still live hold exactly the tokens the burst cached.
     return finished
 
+  def generate_text(self, prompts: Sequence[str], params: SamplingParams | None = None, *,
+                    processor: Any) -> list[tuple[str, GenerationResult]]:
+    """Text in, text out (the reference's `LMInterface.generate` with `input_text`,
+    simply/model_lib.py:4662-4717): `processor` (simply_b200.text.TextProcessor) puts the bos id
+    in front of each encoded prompt and names the eos ids, which end a request unless `params`
+    names stop tokens of its own.  Returns (generated text, result) per prompt; the text leaves
+    out the token that ended the request."""
+    params = params or SamplingParams()
+    if params.stop_token_ids is None:
+      params = dataclasses.replace(params, stop_token_ids=tuple(processor.eos_ids))
+    results = self.generate([processor.encode(p) for p in prompts], params)
+    out = []
+    for r in results:
+      ids = r.output_token_ids
+      if r.finish_reason == "eos" and ids:
+        ids = ids[:-1]
+      out.append((processor.decode(ids), r))
+    return out
+
   def generate(self, prompts: Sequence[Sequence[int]],
                params: SamplingParams | Sequence[SamplingParams] | None = None
                ) -> list[GenerationResult]:
