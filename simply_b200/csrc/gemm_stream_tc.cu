@@ -191,8 +191,21 @@ int weight_map(CUtensorMap* map, const void* w, long long rows, long long cols) 
   return 0;
 }
 
+// The kernel needs more dynamic shared memory than a launch gets by default; said once per kernel,
+// before anything asks how many of its blocks or clusters fit the GPU.
+template <int BNT, int STAGES, int EPI>
+int configure_kernel() {
+  constexpr size_t smem_bytes = (size_t)STAGES * (A_BYTES + BNT * BK * 2) + 1024;
+  static int status = -1;
+  if (status < 0)
+    status = (int)cudaFuncSetAttribute(stream_tc_kernel<BNT, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem_bytes);
+  return status;
+}
+
 template <int BNT, int STAGES, int EPI>
 int max_active_clusters(int ks, size_t smem_bytes) {
+  if (configure_kernel<BNT, STAGES, EPI>() != 0) return 0;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(ks * 64);
   config.blockDim = dim3(THREADS);
@@ -212,12 +225,13 @@ int max_active_clusters(int ks, size_t smem_bytes) {
   return n;
 }
 
-// Blocks of a cluster for a product with `tiles` row tiles: the power of two (at most 8) that
-// brings the launch closest to one block on every SM without a second wave, given how many
-// clusters of each size the GPU holds at once.
+// Blocks of a cluster for a product with `tiles` row tiles: the size (at most 8) that brings the
+// launch closest to one block on every SM without a second wave, given how many clusters of each
+// size the GPU holds at once (clusters live inside one GPC, so a size that does not divide a GPC's
+// SMs leaves some of them out: 18 tiles run as clusters of 6, not of 8).
 template <int BNT, int STAGES, int EPI>
 int choose_split(int tiles, int total_kb, size_t smem_bytes) {
-  static int max_clusters[4] = {-1, -1, -1, -1};  // for cluster sizes 1, 2, 4, 8
+  static int max_clusters[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};  // by cluster size
   static int num_sms = 0;
   if (num_sms == 0) {
     int device = 0;
@@ -225,11 +239,10 @@ int choose_split(int tiles, int total_kb, size_t smem_bytes) {
     if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || num_sms <= 0) num_sms = 1;
   }
   int best = 1, best_blocks = tiles;
-  for (int i = 1; i < 4; ++i) {
-    const int ks = 1 << i;
+  for (int ks = 2; ks <= 8; ++ks) {
     if (total_kb / ks < 4) break;  // every block should have a few stages of k
-    if (max_clusters[i] < 0) max_clusters[i] = max_active_clusters<BNT, STAGES, EPI>(ks, smem_bytes);
-    if (tiles > max_clusters[i]) continue;  // would need a second wave of clusters
+    if (max_clusters[ks] < 0) max_clusters[ks] = max_active_clusters<BNT, STAGES, EPI>(ks, smem_bytes);
+    if (tiles > max_clusters[ks]) continue;  // would need a second wave of clusters
     const int blocks = tiles * ks;
     if (blocks > best_blocks && blocks <= num_sms) {
       best = ks;
@@ -243,20 +256,14 @@ template <int BNT, int STAGES, int EPI>
 int launch_stream(const bf16* x, const bf16* w, void* out, int M, int N, int K, float cap, int act, int split_override,
                   int* err, cudaStream_t stream, const RopeStore& rs) {
   constexpr size_t smem_bytes = (size_t)STAGES * (A_BYTES + BNT * BK * 2) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(stream_tc_kernel<BNT, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem_bytes);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  if (const int e = configure_kernel<BNT, STAGES, EPI>()) return e;
   CUtensorMap map_w, map_x;
   if (weight_map(&map_w, w, N, K) != 0) return -12;
   if (sb_make_map_2d(&map_x, x, M, K, BNT) != 0) return -12;
   const int tiles = EPI == 3 ? N / 128 : (EPI == 2 ? (N / 2 + 63) / 64 : (N + 127) / 128);
   const int total_kb = (K + BK - 1) / BK;
   int ks = EPI == 1 ? 1 : choose_split<BNT, STAGES, EPI>(tiles, total_kb, smem_bytes);
-  if (split_override == 1 || split_override == 2 || split_override == 4 || split_override == 8) ks = split_override;
+  if (split_override >= 1 && split_override <= 8) ks = split_override;
   const int kb_per_block = (total_kb + ks - 1) / ks;
 
   cudaLaunchConfig_t config = {};
@@ -287,29 +294,41 @@ int launch_stream(const bf16* x, const bf16* w, void* out, int M, int N, int K, 
   return 0;
 }
 
+template <int BNT, int DEEP, int SHALLOW, int EPI>
+int launch_stream_depth(const bf16* x, const bf16* w, void* out, int M, int N, int K, float cap, int act,
+                        int split_override, int stages, int* err, cudaStream_t stream, const RopeStore& rs) {
+  // Stages: the deep ring (8; 6 with 128 tokens) gives one block the whole SM; the shallow one
+  // keeps two blocks on an SM (this kernel's and the next one's, which then starts its weights
+  // early).  Measured on the four products of a Gemma 2 2B layer, the deep ring is the faster one
+  // where a block streams a few hundred KB of weights, the shallow one for the small products.
+  bool deep = stages >= 6;
+  if (stages == 0) {
+    const int tiles = EPI == 3 ? N / 128 : (EPI == 2 ? (N / 2 + 63) / 64 : (N + 127) / 128);
+    const int total_kb = (K + BK - 1) / BK;
+    constexpr size_t smem_deep = (size_t)DEEP * (A_BYTES + BNT * BK * 2) + 1024;
+    const int ks = (EPI == 1 || (split_override >= 1 && split_override <= 8))
+                       ? (split_override >= 1 ? split_override : 1)
+                       : choose_split<BNT, DEEP, EPI>(tiles, total_kb, smem_deep);
+    deep = (total_kb + ks - 1) / ks >= 20;
+  }
+  return deep ? launch_stream<BNT, DEEP, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs)
+              : launch_stream<BNT, SHALLOW, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs);
+}
+
 template <int EPI>
 int launch_stream_rows(const bf16* x, const bf16* w, void* out, int M, int N, int K, float cap, int act,
                        int split_override, int stages, int* err, cudaStream_t stream, const RopeStore& rs = RopeStore{}) {
-  // Stages: 8 (6 with 128 tokens) give one block the whole SM; 4 keep two blocks on an SM (this
-  // kernel's and the next one's, which then starts its weights early).  Measured on the four
-  // products of a Gemma 2 2B layer, the deep ring is the faster one for the large products.
-  const bool deep = stages == 0 || stages >= 6;
-  if (M <= 32)
-    return deep ? launch_stream<32, 8, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs)
-                : launch_stream<32, 4, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs);
-  if (M <= 64)
-    return deep ? launch_stream<64, 8, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs)
-                : launch_stream<64, 4, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs);
-  return deep ? launch_stream<128, 6, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs)
-              : launch_stream<128, 3, EPI>(x, w, out, M, N, K, cap, act, split_override, err, stream, rs);
+  if (M <= 32) return launch_stream_depth<32, 8, 4, EPI>(x, w, out, M, N, K, cap, act, split_override, stages, err, stream, rs);
+  if (M <= 64) return launch_stream_depth<64, 8, 4, EPI>(x, w, out, M, N, K, cap, act, split_override, stages, err, stream, rs);
+  return launch_stream_depth<128, 6, 3, EPI>(x, w, out, M, N, K, cap, act, split_override, stages, err, stream, rs);
 }
 
 }  // namespace
 
 // Returns -9 when the shape is outside what the kernel takes (the caller then uses another
 // product): M > 128, K not a multiple of 8, N odd for the gated epilogue, operands not 16-byte aligned.
-// split_override: 0 lets the launch choose how many blocks share a tile's k; 1, 2, 4, 8 fix it (tests).
-// stages: 0 or 8: the deep ring of stages; 4: the shallow one (experiments).
+// split_override: 0 lets the launch choose how many blocks share a tile's k; 1 to 8 fix it (tests).
+// stages: 0 lets the launch choose the depth of the ring of stages; 8 the deep one, 4 the shallow one (tests).
 extern "C" int sb_gemm_stream_tc(const void* x, const void* w, void* out, int M, int N, int K, int epilogue, float cap,
                                  int act, int split_override, int stages, int* err, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;

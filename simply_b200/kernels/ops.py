@@ -174,7 +174,7 @@ class CudaOps:
         name, _, rows = item.partition(":")
         self.mid_rows[name] = int(rows or 128)
     self.mid_split = 0
-    self.mid_stages = 0  # 0 or 8: the deep ring of stages, 4: the shallow one (experiments)
+    self.mid_stages = 0  # 0: the launch chooses the depth of the ring of stages; 8 deep, 4 shallow (tests)
     # The true 32-bit path must not be routed through a reduced-precision matrix mode.
     torch.backends.cuda.matmul.allow_tf32 = False
     self.launches = 0
