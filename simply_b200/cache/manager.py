@@ -193,9 +193,37 @@ class CacheManager:
       else:
         raise TypeError(f"cache {name!r}: unknown kind of need {need!r}")
     self.lengths = np.zeros(max_slots, dtype=np.int64)
+    # Per slot, what the usual decode step asks in one look: up to which length a step may bring
+    # tokens without taking a page (the smallest group's held pages), and from which length on
+    # some group has a page to give back.  Kept current by `_refresh_limits` whenever a slot's
+    # pages change.  `_fast_limits` is False when a need cannot name its release length.
+    self._grow_limit = [0] * max_slots
+    self._release_at = [1 << 62] * max_slots
+    self._fast_limits = all(g.need.release_length(0, page_size) is not None for g in self.groups)
     self.owner: list[object | None] = [None] * max_slots
     self._live = np.zeros(max_slots, dtype=bool)  # owner is not None
     self._free_slots = list(range(max_slots - 1, -1, -1))
+
+  def _release_at_array(self) -> np.ndarray:
+    return np.asarray(self._release_at, dtype=np.int64)
+
+  def _changes_table(self, slot: int, n: int) -> bool:
+    """Whether `n` more tokens take or give back a page of this slot (any group)."""
+    if not self._fast_limits:
+      return True
+    cur = self.lengths[slot]
+    return cur + n > self._grow_limit[slot] or cur >= self._release_at[slot]
+
+  def _refresh_limits(self, slot: int) -> None:
+    if not self._fast_limits:
+      return
+    grow, release = 1 << 62, 1 << 62
+    for g in self.groups:
+      grow = min(grow, int(g.end_page[slot]) * self.page_size)
+      if int(g.first_page[slot]) < int(g.end_page[slot]):
+        release = min(release, g.need.release_length(int(g.first_page[slot]), self.page_size))
+    self._grow_limit[slot] = grow if self.groups else 1 << 62
+    self._release_at[slot] = release
 
   # ---- slots ----------------------------------------------------------------
   @property
@@ -209,6 +237,7 @@ class CacheManager:
     self.owner[slot] = owner
     self._live[slot] = True
     self.lengths[slot] = 0
+    self._refresh_limits(slot)
     for s in self.states.values():
       if s.storage is not None:
         s.storage[slot].zero_()
@@ -223,6 +252,7 @@ class CacheManager:
     self.owner[slot] = None
     self._live[slot] = False
     self.lengths[slot] = 0
+    self._refresh_limits(slot)
     self._free_slots.append(slot)
 
   def length(self, slot: int) -> int:
@@ -233,6 +263,13 @@ class CacheManager:
     """True if the batch `[(slot, new tokens)]` neither takes nor gives back a page in any group
     (the usual decode step).  One vectorised look instead of a plan per slot and group."""
     if not entries:
+      return True
+    if self._fast_limits:
+      lengths, grow, release = self.lengths, self._grow_limit, self._release_at
+      for slot, n in entries:
+        cur = lengths[slot]
+        if cur + n > grow[slot] or cur >= release[slot]:
+          return False
       return True
     slots = np.fromiter((s for s, _ in entries), dtype=np.int64, count=len(entries))
     new = np.fromiter((n for _, n in entries), dtype=np.int64, count=len(entries))
@@ -251,6 +288,8 @@ class CacheManager:
     has to take pages, so that a request that waits never keeps more than its window."""
     if g.window is None and type(g.need) is PagedKVNeed:
       return []  # keeps every token
+    if self._fast_limits and not np.any(self._live & (self.lengths >= self._release_at_array())):
+      return []  # no live request at all has a page to give back
     live = self._live.copy()
     if busy:
       live[list(busy)] = False
@@ -267,11 +306,22 @@ class CacheManager:
       return 0
     short = 0
     busy = {slot for slot, _ in entries}
-    slots = np.fromiter((s for s, _ in entries), dtype=np.int64, count=len(entries))
-    new = np.fromiter((n for _, n in entries), dtype=np.int64, count=len(entries))
+    changing = [(slot, n) for slot, n in entries if self._changes_table(slot, n)]
+    if len(changing) <= 16:
+      for g in self.groups:
+        back = sum(n for _, n in self._idle_releasable(g, busy))
+        take = 0
+        for slot, n in changing:
+          b, t = g.plan(slot, int(self.lengths[slot]), n)
+          back += b
+          take += t
+        short = max(short, take - back - g.pool.num_free)
+      return max(short, 0)
+    slots = np.fromiter((s for s, _ in changing), dtype=np.int64, count=len(changing))
+    new = np.fromiter((n for _, n in changing), dtype=np.int64, count=len(changing))
     cur = self.lengths[slots]
     for g in self.groups:
-      # `PageGroup.plan` for all entries at once.
+      # `PageGroup.plan` for all of them at once.
       first, end = g.first_page[slots], g.end_page[slots]
       new_first = np.minimum(np.maximum(first, g.need.first_needed_page(cur, self.page_size)), end)
       new_end = np.maximum(end, -(-(cur + new) // self.page_size))
@@ -321,22 +371,28 @@ class CacheManager:
     short = self.pages_short(entries)
     if short:
       raise OutOfPages(f"the step lacks {short} page(s)")
+    # Only the entries whose pages change need the books; the others just grow.
+    changing = [(slot, n) for slot, n in entries if self._changes_table(slot, n)]
+    touched = {slot for slot, _ in changing}
     for gi, g in enumerate(self.groups):
       # Every slot gives back before any slot takes, as the pool may need those pages: first the
       # requests outside the step, then the step's own.
       for slot, _ in self._idle_releasable(g, seen):
         back, _ = g.apply(slot, int(self.lengths[slot]), 0)
         self._poison(gi, back)
-      for slot, n in entries:
+        touched.add(slot)
+      for slot, n in changing:
         cur = int(self.lengths[slot])
         n_back, _ = g.plan(slot, cur, 0)
         if n_back:
           back, _ = g.apply(slot, cur, 0)
           self._poison(gi, back)
-      for slot, n in entries:
+      for slot, n in changing:
         g.apply(slot, int(self.lengths[slot]), n)
     for slot, n in entries:
       self.lengths[slot] += n
+    for slot in touched:
+      self._refresh_limits(slot)
 
   def _poison(self, group: int, pages: list[int]) -> None:
     if not self.poison_freed_pages or not pages:

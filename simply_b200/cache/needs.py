@@ -54,6 +54,17 @@ class PagedKVNeed:
       return 0 if self.window is None else max(length - (self.window - 1), 0) // page_size
     return int(self.first_needed_page(np.array([length], dtype=np.int64), page_size)[0])
 
+  def release_length(self, first_page: int, page_size: int) -> int | None:
+    """The smallest number of cached tokens at which a request whose first held page is
+    `first_page` has a page to give back (`first_needed_page` exceeds `first_page`), or None when
+    this need cannot say (the books then ask `first_needed_page` every time).  A very large
+    number means never."""
+    if type(self).first_needed_page is not PagedKVNeed.first_needed_page:
+      return None
+    if self.window is None:
+      return 1 << 62
+    return (first_page + 1) * page_size + (self.window - 1)
+
   def pool_pages(self, *, page_size: int, max_slots: int, max_seq_len: int, all_pages: int,
                  step_tokens: int, burst_tokens: int) -> int:
     """Pages the group's pool needs so that it never runs out before a pool that keeps every

@@ -240,7 +240,7 @@ class DecodeRunner:
     live = len(slots)
     if not 1 <= steps <= self.MAX_BURST:
       raise ValueError(f"a decode burst has 1..{self.MAX_BURST} steps, got {steps}")
-    lengths = np.array([cache.length(s) for s in slots], dtype=np.int64)
+    lengths = cache.lengths[np.asarray(slots, dtype=np.int64)]
     cache.extend([(s, steps) for s in slots])
     # Graphs exist for a few batch sizes only (a capture costs tens of milliseconds, and a batch
     # that shrinks as requests end would need one per size).  The rows up to the next such size

@@ -95,6 +95,7 @@ class Engine:
                                max_seq_len=ec.max_seq_len, eos_ids=eos_ids)
     self._next_id = 0
     self._unseeded = 0  # requests that came without a sampling seed so far
+    self._burst_params = None  # sampling words of the last decode burst's requests
     self.num_steps = 0
     self._decode_runner = None
     if ec.use_cuda_graphs and self.device.type == "cuda" and hasattr(self.ops, "decode_advance"):
@@ -258,10 +259,18 @@ class Engine:
     steps = max(steps, 1)
     while steps > 1 and self.cache.pages_short([(r.slot, steps) for r in requests]):
       steps //= 2
-    params = self.ops.pack_sample_params(
-        [r.params.temperature for r in requests], [r.params.top_k for r in requests],
-        [r.params.top_p for r in requests], [r.params.seed for r in requests],
-        [len(r.tokens) for r in requests])
+    # The sampling words of a batch change only in the position to sample: the rest is kept from
+    # the last burst of the same requests.
+    key = tuple(id(r) for r in requests)
+    if self._burst_params is not None and self._burst_params[0] == key:
+      params = self._burst_params[1].copy()
+      params[:, 5] = [len(r.tokens) for r in requests]
+    else:
+      params = self.ops.pack_sample_params(
+          [r.params.temperature for r in requests], [r.params.top_k for r in requests],
+          [r.params.top_p for r in requests], [r.params.seed for r in requests],
+          [len(r.tokens) for r in requests])
+      self._burst_params = (key, params, requests)  # (the requests are held so that their ids stay theirs)
     want_logprobs = any(r.params.logprobs for r in requests)
     tokens = self._decode_runner.run([r.slot for r in requests], [r.tokens[-1] for r in requests],
                                      params, steps, logprobs=want_logprobs)
