@@ -289,6 +289,31 @@ class Engine:
     # Requests that are still live hold exactly the tokens the burst cached.
     return finished
 
+  def score_tokens(self, tokens: Sequence[int], params: SamplingParams | None = None,
+                   rows_per_step: int = 256) -> list[float]:
+    """The log-likelihood of every token but the first, given the tokens before it: len(tokens) - 1
+    values (the reference's `LMInterface.score_tokens`, simply/model_lib.py:4995-5036).  `params`
+    gives the temperature, top-k and top-p under which a token is scored (default: the plain
+    softmax); a greedy setting scores the most likely token 0 and any other -inf.  The tokens run
+    through the step function in portions of `rows_per_step`, in a slot of their own."""
+    params = params or SamplingParams(temperature=1.0)
+    tokens = [int(t) for t in tokens]
+    if len(tokens) < 2:
+      return []
+    if len(tokens) - 1 > self.engine_config.max_seq_len:
+      raise ValueError(f"{len(tokens)} tokens exceed max_seq_len {self.engine_config.max_seq_len}")
+    slot = self.open_request(("score", id(tokens)))
+    scores: list[float] = []
+    try:
+      for start in range(0, len(tokens) - 1, rows_per_step):
+        portion = tokens[start:min(start + rows_per_step, len(tokens) - 1)]
+        logits = self.step_raw([StepEntry(slot, portion, tuple(range(len(portion))))])
+        targets = torch.tensor(tokens[start + 1:start + 1 + len(portion)], dtype=torch.int32)
+        scores += self.ops.token_logprobs(logits, targets, params.temperature, params.top_k, params.top_p).tolist()
+    finally:
+      self.close_request(slot)
+    return scores
+
   def generate_text(self, prompts: Sequence[str], params: SamplingParams | None = None, *,
                     processor: Any) -> list[tuple[str, GenerationResult]]:
     """Text in, text out (the reference's `LMInterface.generate` with `input_text`,

@@ -763,6 +763,31 @@ class CudaOps:
                  _ptr(step_counter), r, vocab, _ptr(scratch))
     return out
 
+  def token_logprobs(self, logits: torch.Tensor, tokens: torch.Tensor, temperature: float, top_k: int,
+                     top_p: float) -> torch.Tensor:
+    """float32 [R]: the log-likelihood of tokens[r] under row r of `logits` with the sampling masks
+    applied (simply/utils/sampling_lib.py:540-601): a greedy setting scores the argmax 0 and every
+    other token -inf; otherwise the log-softmax of logits / temperature over the kept entries."""
+    r, vocab = logits.shape
+    logits = logits.contiguous()
+    params = self.pack_sample_params([temperature] * r, [top_k] * r, [top_p] * r, [0] * r, [0] * r)
+    dev_params = torch.from_numpy(params).to(self.device, non_blocking=True)
+    slices = self.lib.sb_sample_slices(r, vocab)
+    scratch = self._new(r * (2 + 2 * slices), dtype=torch.int32)
+    drawn = self._new(r, dtype=torch.int32)
+    # (the draw is not used, except for greedy rows, where it is the argmax; the call leaves the
+    # rows' keep-thresholds in `scratch`)
+    self._call("sb_sample", _ptr(logits), _ptr(dev_params), _ptr(drawn), r, vocab, _ptr(scratch))
+    out = self._new(r, dtype=torch.float32)
+    tokens = tokens.to(device=self.device, dtype=torch.int32).contiguous()
+    self._call("sb_sample_logprobs", _ptr(logits), _ptr(dev_params), _ptr(tokens), _ptr(out), None, r, vocab,
+               _ptr(scratch))
+    if temperature == 0 or top_k == 1:
+      out = torch.where(tokens == drawn, out, torch.full_like(out, float("-inf")))
+    else:
+      out = torch.where(out <= -3.0e38, torch.full_like(out, float("-inf")), out)  # a token the masks drop
+    return out
+
   def keep_logits(self, logits: torch.Tensor, history: torch.Tensor, step_counter: torch.Tensor) -> None:
     """history[step_counter] = logits, without the host knowing the step (tests of graph replays)."""
     self._call("sb_keep_logits", _ptr(logits), _ptr(history), _ptr(step_counter), logits.numel())

@@ -165,6 +165,12 @@ class ReferenceOps:
     return out.reshape(t, num_heads * head_dim).to(self.dtype)
 
   # ---- sampling -------------------------------------------------------------
+  def token_logprobs(self, logits, tokens, temperature, top_k, top_p):
+    rows = [logits[i].float().cpu().numpy() for i in range(logits.shape[0])]
+    lp = [plain.token_logprob(rows[i], int(tokens[i]), float(temperature), int(top_k), float(top_p))
+          for i in range(len(rows))]
+    return torch.tensor(lp, dtype=torch.float32, device=logits.device)
+
   def sample(self, logits, temperature, top_k, top_p, seed, position, logprobs=False):
     """logits f32 [R, V]; the other arguments are host sequences of length R."""
     rows = [logits[i].float().cpu().numpy() for i in range(logits.shape[0])]

@@ -105,6 +105,26 @@ def test_logprobs_and_default_seeds(models):
   assert a.output_token_ids == b.output_token_ids == plain.sample(prompts[0], 12, 1.0, 9)
 
 
+def test_score_tokens(models):
+  """simply/model_lib.py:4995-5036: the log-likelihood of each token given those before it, under
+  the plain softmax or under sampling masks; greedy scores the argmax 0 and anything else -inf."""
+  folder, plain, _, _ = models["b"]
+  toks = np.random.default_rng(8).integers(0, plain.cfg["vocab_size"], 37).tolist()
+  eng = cpu_engine(folder, page_size=8)
+  logits = plain.forward(toks)
+  want = [plain_lib.token_logprob(logits[i], toks[i + 1], 1.0, -1, 1.0) for i in range(len(toks) - 1)]
+  got = eng.score_tokens(toks, rows_per_step=7)  # in portions, through the cache
+  np.testing.assert_allclose(got, want, atol=2e-4)
+  assert len(got) == len(toks) - 1 and eng.cache.all_pages_free()
+  masked = eng.score_tokens(toks, SamplingParams(temperature=0.7, top_k=5))
+  want = [plain_lib.token_logprob(logits[i], toks[i + 1], 0.7, 5, 1.0) for i in range(len(toks) - 1)]
+  assert [np.isinf(a) for a in masked] == [np.isinf(b) for b in want] and any(np.isinf(want))
+  np.testing.assert_allclose([a for a in masked if np.isfinite(a)], [b for b in want if np.isfinite(b)], atol=2e-4)
+  greedy_path = toks[:5] + plain.greedy(toks[:5], 6)
+  assert eng.score_tokens(greedy_path, SamplingParams(temperature=0.0))[4:] == [0.0] * 6
+  assert eng.score_tokens([3], None) == []
+
+
 def test_eos_ends_a_request(models):
   folder, plain, _, _ = models["a"]
   prompt = [3, 1, 4, 1, 5]

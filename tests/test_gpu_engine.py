@@ -183,6 +183,24 @@ def test_logprobs_from_eager_steps_and_from_graph_bursts(folders):
     np.testing.assert_allclose(r.output_token_logprobs, want, atol=3e-4)
 
 
+def test_score_tokens_on_the_gpu(folders):
+  from tests.plain import gemma2_plain as plain_lib
+  plain = PlainGemma2(folders["b"])
+  toks = prompts_for(plain, (90,), seed=33)[0]
+  logits = plain.forward(toks)
+  eng = engine_for(folders["b"], "float32")
+  want = [plain_lib.token_logprob(logits[i], toks[i + 1], 1.0, -1, 1.0) for i in range(len(toks) - 1)]
+  np.testing.assert_allclose(eng.score_tokens(toks, rows_per_step=32), want, atol=3e-4)
+  masked = eng.score_tokens(toks, SamplingParams(temperature=0.8, top_k=10, top_p=0.9))
+  want = [plain_lib.token_logprob(logits[i], toks[i + 1], 0.8, 10, 0.9) for i in range(len(toks) - 1)]
+  assert [np.isinf(a) for a in masked] == [np.isinf(b) for b in want]
+  np.testing.assert_allclose([a for a in masked if np.isfinite(a)], [b for b in want if np.isfinite(b)], atol=3e-4)
+  greedy_path = toks[:9] + plain.greedy(toks[:9], 5)
+  assert eng.score_tokens(greedy_path, SamplingParams(temperature=0.0))[8:] == [0.0] * 5
+  eng.ops.check_errors()
+  assert eng.cache.all_pages_free()
+
+
 def test_a_float32_folder_served_in_bfloat16(tmp_path):
   """Matrices stored in 32 bits are narrowed to the activation dtype on load
   (simply/utils/checkpoint_lib.py:658-670): the engine holds bfloat16 matrices, runs the bfloat16
