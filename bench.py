@@ -277,6 +277,31 @@ def time_kernels(engine, torch, cfg, batch, context, peaks):
   gbs = weight_bytes / (ms * 1e-3) / 1e9
   out[f"decode_products_b{batch}"] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4)}
 
+  # The same four products for serving batches of 24 and 64 rows, replayed from a CUDA graph of all
+  # layers (as the decode graphs run them: launch costs off the clock).  24 rows take the engine's
+  # own tcgen05 product, 64 rows the library's.
+  side = torch.cuda.Stream(device=dev)
+  for rows in (24, 64):
+    xs = [torch.randn(rows, k, device=dev).to(torch.bfloat16) for k in (d, hq * dh, f)]
+
+    def serving_products():
+      for b in blocks:
+        ops.linear(xs[0], b.mixer.qkv_weight)
+        ops.linear(xs[1], b.mixer.o_proj.weight)
+        ops.gated_linear(xs[0], b.feed_forward.gate_up_weight, b.feed_forward.activation)
+        ops.linear(xs[2], b.feed_forward.down_proj.weight)
+
+    with torch.cuda.stream(side), ops.hold_stream():
+      serving_products()
+      torch.cuda.synchronize()
+      graph = torch.cuda.CUDAGraph()
+      graph.capture_begin()
+      serving_products()
+      graph.capture_end()
+      ms = timed(graph.replay)
+    gbs = weight_bytes / (ms * 1e-3) / 1e9
+    out[f"decode_products_b{rows}"] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4)}
+
   # Attention of a decode step: the cache is made to hold the context without computing it
   # (the kernel's time does not depend on what the pages hold).
   slots = [engine.open_request(f"k{i}") for i in range(batch)]

@@ -476,17 +476,12 @@ def test_tcgen05_prefill_long_walks(table, hq, hkv, dh, ps, window, cap):
   scores spread so widely that the running maximum moves and O is rescaled again and again.
   Run a few times: a hand-over that can miss a phase shows as a timed-out wait or a wrong row."""
   dtype = torch.bfloat16
-  ops = table[dtype]
+  ops, ref = table[dtype], ReferenceOps(dtype)
   seqs = [(700, 1900), (0, 130), (64, 1)]
   sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=dtype,
                      device="cuda", ops=ops, seed=11)
   q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 3.0).to(dtype).cuda()
-  ops.tensor_core_attention = False
-  try:
-    want = run_attention(ops, q, sc, hq, hkv, dh, cap, window)  # the general kernel
-  finally:
-    ops.tensor_core_attention = True
-  ops.check_errors()
+  want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)  # the plain statement
   for _ in range(4):
     sc.ctx.memo.clear()
     got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
