@@ -81,6 +81,8 @@ class DecodeRunner:
     self.stream = torch.cuda.Stream(device=engine.device)
     self._stream_ptr = ctypes.c_void_p(self.stream.cuda_stream)
     self.pool = torch.cuda.graph_pool_handle()
+    self.bursts = 0  # bursts run so far, and how many of them went on from the device's own state
+    self.resumed_bursts = 0
     self.h2d_bytes = 0  # bytes copied to and from the device by `run` so far
     self.d2h_bytes = 0
 
@@ -281,6 +283,8 @@ class DecodeRunner:
       ranges = self._chunk_ranges(g, lengths, steps)
       resumed = follows and self._same_ranges(r["ranges"], ranges)
     first_row = r["counter"] if resumed else 0
+    self.bursts += 1
+    self.resumed_bursts += bool(resumed)
     h = g.host.numpy()
 
     def put(name, values):
