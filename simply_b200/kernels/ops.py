@@ -167,6 +167,12 @@ class CudaOps:
     # takes up to 128 rows; measured inside decode steps of the Gemma 2 2B shape it is ahead of
     # the library's products up to 32 rows (by 1 to 2 % of the step) and behind them from 33
     # (by 1 to 4 %), so that is where the line is drawn.
+    # From this many tokens the gated feed-forward product runs on the engine's own tcgen05 kernel
+    # with the activation on the accumulators (csrc/gemm_gated_tc.cu); below, and for shapes it
+    # does not take, the library's product and a pass of its own for the activation.  0: never.
+    self.gated_tc_min_rows = int(os.environ.get("SIMPLY_B200_GATED_TC_MIN_ROWS", "256"))
+    self.gated_tc_blocks = 0  # 0: one block per SM (tests: fewer, so that blocks walk many tiles)
+    self.gated_tc_pairs = True  # blocks work in pairs on tiles of 256 tokens (False: each alone on 128; tests)
     self.mid_rows = {"qkv": 32, "gated": 32, "plain": 32, "head": 32}
     env = os.environ.get("SIMPLY_B200_SERVING_BATCH_PRODUCT")  # experiments: "qkv:128,gated:32,plain:0,head:128"
     if env:
@@ -199,6 +205,7 @@ class CudaOps:
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
         "sb_gemm_stream_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                               c_void, c_void],
+        "sb_gemm_gated_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void],
         "sb_qkv_rope_stream_tc": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
                                   c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_int, c_int, c_void],
         "sb_qkv_rope_skinny": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
@@ -532,6 +539,12 @@ class CudaOps:
         and self.skinny_max_rows < m <= self.mid_rows["gated"] and x.is_contiguous() and w_gate_up.is_contiguous()):
       out = self._new(m, n // 2, dtype=torch.bfloat16)
       if self._mid_product(x, w_gate_up, out, 2, activation=activation):
+        return out
+    if (w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m >= self.gated_tc_min_rows > 0
+        and x.is_contiguous() and w_gate_up.is_contiguous()):
+      out = self._new(m, n // 2, dtype=torch.bfloat16)
+      if self._call("sb_gemm_gated_tc", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n // 2, k, activation,
+                    self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(self.err)) == 0:
         return out
     return self.gated_activation(self.linear(x, w_gate_up), activation)
 

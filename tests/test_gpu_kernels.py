@@ -342,6 +342,33 @@ def test_gated_linear(table, m, f, k, act):
       torch.testing.assert_close(got.float().cpu(), want.float().cpu(), atol=2e-2, rtol=3.2 * 2.0 ** -8)
 
 
+@pytest.mark.parametrize("pairs", [False, True])
+@pytest.mark.parametrize("blocks", [0, 4])
+@pytest.mark.parametrize("m,f,k,act", [(128, 128, 64, 0), (300, 384, 72, 1), (129, 256, 1032, 2), (1000, 1152, 2304, 0),
+                                       (2048, 2304, 328, 0), (515, 640, 520, 1)])
+def test_gated_product_for_many_tokens(table, pairs, blocks, m, f, k, act):
+  """The tcgen05 product with the activation on its accumulators, by single blocks and by pairs of
+  blocks: token counts that end inside a tile (or leave a pair's second block without a row), k
+  that ends inside a stage, and so few blocks that each walks many tiles (both accumulators and
+  every stage of the ring are used again and again)."""
+  torch.manual_seed(m + f + k)
+  ops, ref = table[torch.bfloat16], ReferenceOps(torch.bfloat16)
+  x = torch.randn(m, k).to(torch.bfloat16)
+  w = (torch.randn(2 * f, k) / k ** 0.5 * 2).to(torch.bfloat16)
+  kept = ops.gated_tc_min_rows, ops.gated_tc_blocks, ops.gated_tc_pairs
+  ops.gated_tc_min_rows, ops.gated_tc_blocks, ops.gated_tc_pairs = 1, blocks, pairs
+  before = ops.launches
+  try:
+    got = ops.gated_linear(x.cuda(), w.cuda(), act)
+  finally:
+    ops.gated_tc_min_rows, ops.gated_tc_blocks, ops.gated_tc_pairs = kept
+  ops.check_errors()
+  assert ops.launches - before == 1, "the product and its activation are one kernel"
+  # see test_gated_linear for the bound
+  torch.testing.assert_close(got.float().cpu(), ref.gated_linear(x, w, act).float().cpu(), atol=2e-2,
+                             rtol=3.2 * 2.0 ** -8)
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("r,v,k,cap", [(1, 1000, 96, 10.0), (7, 256, 64, 30.0), (45, 1003, 72, 0.0), (3, 25600, 2304, 30.0),
                                        (40, 2048, 72, 30.0), (64, 25601, 2304, 30.0), (33, 130, 1000, 0.0), (100, 5000, 96, 30.0),
