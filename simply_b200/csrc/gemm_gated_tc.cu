@@ -40,58 +40,93 @@ constexpr int STAGES = 4;
 constexpr int EPI_WARPS = 8;  // two per 32-lane quarter of tensor memory, 64 features each
 constexpr int THREADS = (2 + EPI_WARPS) * 32;
 constexpr int ACC_COLS = 2 * BF;  // columns of one accumulator
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024;
+// Results leave through shared memory: a warp's 32 tokens x 64 features (rows of 128 bytes, 128-byte
+// swizzle) go out as one TMA store of whole lines.  (Stored straight from registers, 16 bytes per
+// lane at a row's stride, they cost the kernel 7 % more time than the loads and products alone.)
+constexpr int OUT_WARP_BYTES = 32 * 128;
+constexpr int OUT_BYTES = EPI_WARPS * OUT_WARP_BYTES;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + OUT_BYTES + 1024;
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// A block's (or pair's) walk over its tiles and their blocks of k, without a division per step.
+struct TileWalk {
+  int tile, stride, tiles_m, nkb, rows;  // rows: tokens of a tile
+  int m0, f0, kb;
+  __device__ TileWalk(int first, int stride_, int tiles_m_, int nkb_, int rows_)
+      : tile(first), stride(stride_), tiles_m(tiles_m_), nkb(nkb_), rows(rows_), kb(0) {
+    place();
+  }
+  __device__ void place() { m0 = (tile % tiles_m) * rows, f0 = (tile / tiles_m) * BF; }
+  __device__ void next() {
+    if (++kb == nkb) {
+      kb = 0;
+      tile += stride;
+      place();
+    }
+  }
+};
+
 // The gate's activation.  The tanh form of GELU is written as g / (1 + exp(-2 y)) with
 // y = sqrt(2 / pi) (g + 0.044715 g^3), which is the same function (0.5 (1 + tanh y) = 1 / (1 + exp(-2 y)))
-// at two special-function instructions instead of a library tanh; both are exact to a few units
-// in the last place of float32, far below the bfloat16 rounding that follows.
+// at two special-function instructions (ex2, rcp) instead of a library tanh; both are exact to a
+// few units in the last place of float32, far below the bfloat16 rounding that follows.
 __device__ __forceinline__ float gate_act(float g, int act) {
   if (act == 0) {
-    const float y = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
-    return __fdividef(g, 1.0f + exp2f(-2.0f * 1.4426950408889634f * y));
+    constexpr float A = -2.0f * 1.4426950408889634f * 0.7978845608028654f;  // exp(-2 y) = 2^(g (A + B g^2))
+    constexpr float B = A * 0.044715f;
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(g * fmaf(g * g, B, A)));
+    return __fdividef(g, 1.0f + e);
   }
   return sbg::gated_act(g, act);
 }
 
-// One thread's row of a tile: gate and up sums of the features [c0, c1) from the accumulator at
-// `acc` (this warp's lanes), the activation, bfloat16 results to out[row, f0 + c0 ..].  Every lane
-// takes part in the warp-wide tensor-memory loads; only rows of the matrix store.
-__device__ __forceinline__ void store_gated_rows(uint32_t acc, int c0, int c1, int row, int M, int F, int f0,
-                                                 bf16* __restrict__ out, int act) {
-  bf16* orow = out + (size_t)row * F + f0;
+// A warp's part of a tile: 32 tokens (this warp's lanes of tensor memory) x 64 features from
+// feature c0 of the tile.  Gate and up sums from the accumulator at `acc`, the activation,
+// bfloat16 results to the warp's own 4 KB of shared memory (`stage`: 32 rows of 128 bytes, 16-byte
+// pieces swizzled as the TMA expects), then one TMA store to out[row0.., f0 + c0..].
+__device__ __forceinline__ void store_gated_rows(uint32_t acc, int c0, unsigned char* stage, const CUtensorMap* map_out,
+                                                 int row0, int f0, int act) {
+  const int lane = threadIdx.x & 31;
+  if (lane == 0) tma_store_wait_read();  // the store of the tile before has read the stage
+  __syncwarp();
 #pragma unroll 1
-  for (int c = c0; c < c1; c += 16) {
+  for (int c = 0; c < BF / 2; c += 16) {
     uint32_t g[16], u[16];
-    tmem_load_32x16(acc + c, g);
-    tmem_load_32x16(acc + BF + c, u);
+    tmem_load_32x16(acc + c0 + c, g);
+    tmem_load_32x16(acc + BF + c0 + c, u);
     tmem_wait_load();
     uint32_t packed[8];
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
       // The projections are rounded to bfloat16 before the activation, as a product that
-      // stores them would.
-      const float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[i])));
-      const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[i + 1])));
-      const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
-      const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i + 1])));
+      // stores them would (two per conversion; a bfloat16 is the upper half of its float32).
+      const uint32_t gp = pack_bf16(__uint_as_float(g[i]), __uint_as_float(g[i + 1]));
+      const uint32_t up = pack_bf16(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
+      const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
+      const float u0 = __uint_as_float(up << 16), u1 = __uint_as_float(up & 0xFFFF0000u);
       packed[i / 2] = pack_bf16(gate_act(g0, act) * u0, gate_act(g1, act) * u1);
     }
-    if (row < M) {
-      *reinterpret_cast<uint4*>(orow + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      *reinterpret_cast<uint4*>(orow + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    }
+    unsigned char* srow = stage + lane * 128;
+    const int piece = c / 8;  // 16-byte pieces of the row: two per 16 features
+    *reinterpret_cast<uint4*>(srow + ((piece ^ (lane & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    *reinterpret_cast<uint4*>(srow + (((piece + 1) ^ (lane & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+  }
+  fence_proxy_async();  // the rows are visible to the TMA
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map_out, stage, f0 + c0, row0);
+    tma_store_commit();
   }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
 gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                bf16* __restrict__ out, int M, int F, int K, int act, int* err) {
+                const __grid_constant__ CUtensorMap map_out, int M, int F, int K, int act, int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -119,26 +154,43 @@ gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_slot;
-  pdl_wait_block();  // x is written by the kernel before this one, and out may still be read by it
-  pdl_launch_dependents();
+  // What the kernel before this one wrote (x) or may still read (out) is only touched by the
+  // producer and the epilogue warps: they wait for it, the rest of the set-up ran beside it.
 
   if (warp == 0 && lane == 0) {
     // ---- producer -------------------------------------------------------------------------
-    int it = 0;  // stages filled so far, over all tiles
-    for (int tile = blockIdx.x; tile < num_tiles && !s_failed; tile += gridDim.x) {
-      const int m0 = (tile % tiles_m) * BM, f0 = (tile / tiles_m) * BF;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
-        const int s = it % STAGES;
-        if (it >= STAGES && !mbar_wait_bounded(&empty[s], (it / STAGES - 1) & 1)) {
-          s_failed = 1;
-          break;
-        }
-        unsigned char* stage = tiles + s * STAGE_BYTES;
-        mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(stage, &map_x, kb * BK, m0, &full[s]);
-        tma_load_2d(stage + A_BYTES, &map_w, kb * BK, f0, &full[s]);
-        tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, kb * BK, F + f0, &full[s]);
+    // Weights depend on no earlier kernel: those of the first stages are asked for before
+    // `griddepcontrol.wait`, x after it.  (Only this thread waits and triggers: everything the
+    // other warps do follows from its loads, and many threads polling for a long kernel before
+    // them slow that kernel down.)
+    const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    const int total = my_tiles * nkb, pre = min(total, STAGES);
+    TileWalk at(blockIdx.x, gridDim.x, tiles_m, nkb, BM);
+    auto load_w = [&](const TileWalk& w, int s) {
+      unsigned char* stage = tiles + s * STAGE_BYTES;
+      tma_load_2d(stage + A_BYTES, &map_w, w.kb * BK, w.f0, &full[s]);
+      tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, w.kb * BK, F + w.f0, &full[s]);
+    };
+    auto load_x = [&](const TileWalk& w, int s) {
+      tma_load_2d(tiles + s * STAGE_BYTES, &map_x, w.kb * BK, w.m0, &full[s]);
+    };
+    TileWalk first = at;
+    for (int it = 0; it < pre; ++it, at.next()) {
+      mbar_arrive_expect_tx(&full[it], STAGE_BYTES);
+      load_w(at, it);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int it = 0; it < pre; ++it, first.next()) load_x(first, it);
+    for (int it = pre, s = pre % STAGES, use = pre / STAGES; it < total; ++it, at.next()) {
+      if (!mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
+        s_failed = 1;
+        break;
       }
+      mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+      load_w(at, s);
+      load_x(at, s);
+      if (++s == STAGES) s = 0, ++use;
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issue ---------------------------------------------------------------------------
@@ -179,21 +231,23 @@ gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // A warp may only touch the 32 lanes of tensor memory that (warp % 4) names.
     const int quarter = warp & 3, c0 = ((warp - 2) >> 2) * (BF / 2);
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    unsigned char* out_stage = tiles + STAGES * STAGE_BYTES + (warp - 2) * OUT_WARP_BYTES;
     int t = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
       const int m0 = (tile % tiles_m) * BM, f0 = (tile / tiles_m) * BF;
-      if (!mbar_wait_bounded(&acc_full[buf], (t / 2) & 1)) {
+      if (!mbar_wait_bounded_relaxed(&acc_full[buf], (t / 2) & 1)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, c0 + BF / 2, m0 + quarter * 32 + lane, M, F, f0, out, act);
+      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, out_stage, &map_out, m0 + quarter * 32, f0, act);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) tma_store_wait_all();
     if (!ok) s_failed = 1;
   }
   tc_fence_before_sync();
@@ -212,11 +266,11 @@ gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 //   the epilogue warps of both blocks arrive at rank 0's acc_empty[b].
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2;
-constexpr size_t PAIR_SMEM_BYTES = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+constexpr size_t PAIR_SMEM_BYTES = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + OUT_BYTES + 1024;
 
 __global__ void __launch_bounds__(THREADS, 1)
 gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                     bf16* __restrict__ out, int M, int F, int K, int act, int* err) {
+                     const __grid_constant__ CUtensorMap map_out, int M, int F, int K, int act, int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full[PAIR_STAGES], empty[PAIR_STAGES], acc_full[2], acc_empty[2];
@@ -247,27 +301,37 @@ gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   cluster_sync_all();  // the other block's barriers and tensor memory exist before anything arrives there
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_slot;
-  pdl_wait_block();
-  pdl_launch_dependents();
 
   if (warp == 0 && lane == 0) {
     // ---- producer (both blocks) ------------------------------------------------------------
-    int it = 0;
-    for (int tile = pair; tile < num_tiles && !s_failed; tile += num_pairs) {
-      const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, f0 = (tile / tiles_m) * BF;
-      const int w_row = rank == 0 ? f0 : F + f0;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
-        const int s = it % PAIR_STAGES;
-        if (it >= PAIR_STAGES && !mbar_wait_bounded_cluster(&empty[s], (it / PAIR_STAGES - 1) & 1)) {
-          s_failed = 1;
-          break;
-        }
-        unsigned char* stage = tiles + s * PAIR_STAGE_BYTES;
-        const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
-        if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * PAIR_STAGE_BYTES);
-        tma_load_2d_pair(stage, &map_x, kb * BK, m0, bar);
-        tma_load_2d_pair(stage + A_BYTES, &map_w, kb * BK, w_row, bar);
+    // As above: weights of the first stages before `griddepcontrol.wait`, x after it.
+    const int my_tiles = pair < num_tiles ? (num_tiles - 1 - pair) / num_pairs + 1 : 0;
+    const int total = my_tiles * nkb, pre = min(total, PAIR_STAGES);
+    TileWalk at(pair, num_pairs, tiles_m, nkb, 2 * BM);
+    const uint32_t full0 = mapa_shared(smem_u32(&full[0]), 0);  // rank 0's full[0]; the others follow at 8 bytes each
+    auto load_w = [&](const TileWalk& w, int s) {
+      tma_load_2d_pair(tiles + s * PAIR_STAGE_BYTES + A_BYTES, &map_w, w.kb * BK, rank == 0 ? w.f0 : F + w.f0, full0 + 8 * s);
+    };
+    auto load_x = [&](const TileWalk& w, int s) {
+      tma_load_2d_pair(tiles + s * PAIR_STAGE_BYTES, &map_x, w.kb * BK, w.m0 + rank * BM, full0 + 8 * s);
+    };
+    TileWalk first = at;
+    for (int it = 0; it < pre; ++it, at.next()) {
+      if (rank == 0) mbar_arrive_expect_tx(&full[it], 2 * PAIR_STAGE_BYTES);
+      load_w(at, it);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int it = 0; it < pre; ++it, first.next()) load_x(first, it);
+    for (int it = pre, s = pre % PAIR_STAGES, use = pre / PAIR_STAGES; it < total; ++it, at.next()) {
+      if (!mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
+        s_failed = 1;
+        break;
       }
+      if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * PAIR_STAGE_BYTES);
+      load_w(at, s);
+      load_x(at, s);
+      if (++s == PAIR_STAGES) s = 0, ++use;
     }
   } else if (warp == 1 && lane == 0 && rank == 0) {
     // ---- MMA issue (rank 0, for the pair) -----------------------------------------------------
@@ -286,7 +350,7 @@ gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       const uint32_t d = tmem + buf * ACC_COLS;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % PAIR_STAGES;
-        if (!mbar_wait_bounded_cluster(&full[s], (it / PAIR_STAGES) & 1)) {
+        if (!mbar_wait_bounded(&full[s], (it / PAIR_STAGES) & 1)) {
           ok = false;
           break;
         }
@@ -304,21 +368,23 @@ gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     // ---- epilogue (both blocks, each its own 128 tokens) ----------------------------------------
     const int quarter = warp & 3, c0 = ((warp - 2) >> 2) * (BF / 2);
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    unsigned char* out_stage = tiles + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * OUT_WARP_BYTES;
     int t = 0;
     bool ok = true;
     for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++t) {
       const int buf = t & 1;
       const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, f0 = (tile / tiles_m) * BF;
-      if (!mbar_wait_bounded_cluster(&acc_full[buf], (t / 2) & 1)) {
+      if (!mbar_wait_bounded_relaxed(&acc_full[buf], (t / 2) & 1)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, c0 + BF / 2, m0 + quarter * 32 + lane, M, F, f0, out, act);
+      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, out_stage, &map_out, m0 + quarter * 32, f0, act);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[buf]), 0));
     }
+    if (lane == 0) tma_store_wait_all();
     if (!ok) s_failed = 1;
   }
   tc_fence_before_sync();
@@ -396,9 +462,10 @@ extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, 
     }
   }
   if (configured != 0) return configured;
-  CUtensorMap map_x, map_w;
+  CUtensorMap map_x, map_w, map_out;
   if (weight_map(&map_w, w, 2LL * F, K) != 0) return -12;
   if (sb_make_map_2d(&map_x, x, M, K, BM) != 0) return -12;
+  if (sb_make_map_2d(&map_out, out, M, F, 32) != 0) return -12;
   if (pairs && max_pairs > 0) {
     const int num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * (F / BF);
     const int n = min(num_tiles, blocks > 0 ? max(blocks / 2, 1) : max_pairs);
@@ -421,15 +488,15 @@ extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, 
     ++n_attr;
     config.attrs = attribute;
     config.numAttrs = n_attr;
-    cudaError_t e = cudaLaunchKernelEx(&config, gated_tc_pair_kernel, map_x, map_w, (bf16*)out, M, F, K, act, err);
+    cudaError_t e = cudaLaunchKernelEx(&config, gated_tc_pair_kernel, map_x, map_w, map_out, M, F, K, act, err);
     if (e != cudaSuccess) return (int)e;
     SB_LAUNCH_CHECK();
     return 0;
   }
   const int num_tiles = ((M + BM - 1) / BM) * (F / BF);
   const int grid = min(num_tiles, blocks > 0 ? blocks : num_sms);
-  cudaError_t e = sb_launch(gated_tc_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, map_x, map_w, (bf16*)out, M,
-                            F, K, act, err);
+  cudaError_t e = sb_launch_early(gated_tc_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, map_x, map_w,
+                                  map_out, M, F, K, act, err);
   if (e != cudaSuccess) return (int)e;
   SB_LAUNCH_CHECK();
   return 0;

@@ -56,6 +56,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
   }
 }
 
+// The same for a waiter with time to spare (an epilogue that has a whole tile's products to wait
+// for): it sleeps between tries instead of polling, which leaves the issue slots, and the power
+// they draw, to the warps that feed the tensor core.
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t* bar, unsigned parity) {
+  unsigned long long start = 0;
+  for (unsigned tries = 1;; ++tries) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(128);
+    if ((tries & 0xFFu) == 0) {
+      const unsigned long long now = sb_global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 500000000ull) return false;
+    }
+  }
+}
+
 // ---- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
@@ -71,6 +87,17 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
       : "memory");
 }
+// A tile from shared memory to the tensor (rows and columns beyond it are not written).  The
+// issuing thread commits its copies as a group and waits for the group: `_read` until shared
+// memory may be written again, `_all` until the copies are complete.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(map),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 // ---- tensor memory and tcgen05 -------------------------------------------------------------------
