@@ -99,7 +99,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __global__ void __launch_bounds__(TC_THREADS)
 attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_q,
-                       const __grid_constant__ CUtensorMap map_kv) {
+                       const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_out) {
   pdl_wait();
   pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -459,6 +459,11 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     }
     if (ok && !mbar_wait_bounded(&o_done, 0)) ok = false;
     tc_fence_after_sync();
+    // A full tile leaves through shared memory (the key stages, free by now) in the layout Q came
+    // in, as TMA stores of whole lines: stored straight from registers, 16 bytes per lane at a
+    // row's stride, the 64 KB of a tile took 3.7 us of a block's time.  A tile that ends with its
+    // sequence is stored row by row: a box would reach into the next sequence's rows.
+    const bool staged = rows_valid == BM;
     if (ok) {
       // Every lane takes part in the warp-wide tensor-memory loads; only rows of the sequence store.
       const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -469,17 +474,33 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         uint32_t o[16];
         tmem_load_32x16(tmem + lane_base + O_COL0 + c, o);
         tmem_wait_load();
-        if (valid) {
+        uint4 v[2];
 #pragma unroll
-          for (int i = 0; i < 16; i += 8) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c + i) = v;
-          }
+        for (int i = 0; i < 2; ++i) {
+          v[i].x = pack_bf16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+          v[i].y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+          v[i].z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+          v[i].w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
         }
+        if (staged) {
+          // slab of 64 dims, row of 128 bytes, 16-byte pieces swizzled as the TMA expects
+          unsigned char* srow = sk + (c / 64) * (BM * 128) + r * 128;
+          const int piece = (c % 64) / 8;
+          *reinterpret_cast<uint4*>(srow + ((piece ^ (r & 7)) << 4)) = v[0];
+          *reinterpret_cast<uint4*>(srow + (((piece + 1) ^ (r & 7)) << 4)) = v[1];
+        } else if (valid) {
+          *reinterpret_cast<uint4*>(op + c) = v[0];
+          *reinterpret_cast<uint4*>(op + c + 8) = v[1];
+        }
+      }
+    }
+    if (staged) {  // the same for every thread of the block, whether its waits ran out or not
+      fence_proxy_async();
+      asm volatile("bar.sync 1, %0;\n" ::"n"(128 * GROUPS * SPLIT) : "memory");  // the softmax warps
+      if (warp == 4 && lane == 0 && !s_failed) {
+        for (int sl = 0; sl < SLABS; ++sl) tma_store_3d(&map_out, sk + sl * (BM * 128), sl * 64, m * group, row0 + i0);
+        tma_store_commit();
+        tma_store_wait_all();
       }
     }
     if (!ok) s_failed = 1;
@@ -513,13 +534,13 @@ extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const
   if (group > BM || BM % group || (page_size & (page_size - 1))) return -11;
   SbEncodeTiled encode = sb_encode_tiled();
   if (!encode) return -12;
-  CUtensorMap map_q, map_kv;
-  {
+  CUtensorMap map_q, map_kv, map_out;
+  for (int which = 0; which < 2; ++which) {  // q and out have the same shape
     const cuuint64_t dims[3] = {(cuuint64_t)DH, (cuuint64_t)num_q_heads, (cuuint64_t)num_tokens};
     const cuuint64_t strides[2] = {(cuuint64_t)DH * 2, (cuuint64_t)num_q_heads * DH * 2};
     const cuuint32_t box[3] = {64u, (cuuint32_t)group, (cuuint32_t)(BM / group)};
     const cuuint32_t elem[3] = {1u, 1u, 1u};
-    if (encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+    if (encode(which == 0 ? &map_q : &map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, which == 0 ? const_cast<void*>(q) : out, dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return -12;
@@ -537,7 +558,7 @@ extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  sb_launch(attn_prefill_tc_kernel, dim3(num_items, num_kv_heads), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv);
+  sb_launch(attn_prefill_tc_kernel, dim3(num_items, num_kv_heads), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv, map_out);
   SB_LAUNCH_CHECK();
   return 0;
 }
