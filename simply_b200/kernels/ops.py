@@ -170,7 +170,7 @@ class CudaOps:
     # From this many tokens the gated feed-forward product runs on the engine's own tcgen05 kernel
     # with the activation on the accumulators (csrc/gemm_gated_tc.cu); below, and for shapes it
     # does not take, the library's product and a pass of its own for the activation.  0: never.
-    self.gated_tc_min_rows = int(os.environ.get("SIMPLY_B200_GATED_TC_MIN_ROWS", "256"))
+    self.gated_tc_min_rows = int(os.environ.get("SIMPLY_B200_GATED_TC_MIN_ROWS", "129"))
     self.gated_tc_blocks = 0  # 0: one block per SM (tests: fewer, so that blocks walk many tiles)
     # Blocks work in pairs (tcgen05 cta_group::2, tiles of 256 tokens) or each alone on tiles of 128.
     # None: by the size of the product: measured at the Gemma 2 shapes, pairs are ahead (by 1 to
