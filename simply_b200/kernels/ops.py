@@ -261,7 +261,7 @@ class CudaOps:
 
   def _call(self, name: str, *args) -> int:
     rc = getattr(self.lib, name)(*args, self._stream())
-    self.launches += 1
+    self.launches += rc != -9  # -9: the kernel does not take the shape and launched nothing
     if rc != 0 and rc != -9:
       why = _STATUS.get(rc, f"CUDA error {rc}" if rc > 0 else f"status {rc}")
       raise KernelError(f"{name}: {why}")
