@@ -36,7 +36,7 @@ class KernelBuildError(RuntimeError):
 
 
 # Sources that are compiled once per head size (-DSB_HEAD_DIM=N) into libraries of their own.
-PER_HEAD_DIM = ("attention_mma.cu", "attention_tc.cu")
+PER_HEAD_DIM = ("attention_mma.cu", "attention_tc.cu", "attention_tc_pair.cu")
 
 
 def sources() -> list[str]:

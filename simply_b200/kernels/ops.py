@@ -154,6 +154,9 @@ class CudaOps:
     # Prefill attention on the tcgen05 tensor cores where the shapes allow (head size a multiple of
     # 64, group dividing 128, page size a power of two); False keeps the mma.sync kernel.
     self.prefill_tcgen05 = True
+    # ... and there by pairs of blocks (cta_group::2) where the shapes allow (head size 128 or 256,
+    # pages of at least 64 tokens); False keeps single blocks (tests).
+    self.prefill_pairs = True
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
     self.skinny_warps = 0
@@ -315,13 +318,19 @@ class CudaOps:
         prefill_tc.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                c_int, c_float, c_int, c_void, c_int, c_void, c_void]
         prefill_tc.restype = c_int
+      prefill_pair = None
+      if head_dim in (128, 256):
+        prefill_pair = getattr(lib, f"sb_attn_prefill_pair_hd{head_dim}")
+        prefill_pair.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                                 c_int, c_float, c_int, c_void, c_int, c_void, c_void]
+        prefill_pair.restype = c_int
       resident = getattr(lib, f"sb_attn_decode_resident_hd{head_dim}")
       resident.argtypes, resident.restype = [c_int], c_int
       slots = resident(1)
       if slots <= 0:
         raise KernelError(f"sb_attn_decode_resident: {_STATUS.get(slots, slots)}")
       self._decode_slots[head_dim] = slots
-      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc)
+      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair)
     return fns
 
   def decode_chunk_for(self, kv_lo: Sequence[int], kv_hi: Sequence[int], num_kv_heads: int, head_dim: int) -> int:
@@ -407,12 +416,24 @@ class CudaOps:
     return (self.prefill_tcgen05 and head_dim % 64 == 0 and 128 % group == 0
             and page_size & (page_size - 1) == 0)
 
+  def _prefill_uses_pairs(self, head_dim: int, group: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel by pairs of blocks (csrc/attention_tc_pair.cu)."""
+    return (self.prefill_pairs and self._prefill_uses_tcgen05(head_dim, group, page_size)
+            and head_dim in (128, 256) and page_size >= 64)
+
+  def _prefill_rows(self, head_dim: int, group: int, page_size: int) -> int:
+    """Query rows of a prefill work item: 256 for a pair of blocks, 128 for the tcgen05 kernel, else the mma.sync tile."""
+    if self._prefill_uses_pairs(head_dim, group, page_size):
+      return 256
+    if self._prefill_uses_tcgen05(head_dim, group, page_size):
+      return 128
+    return self.prefill_rows or 64
+
   def _plan_key(self, window: int | None, group: int, num_kv_heads: int, head_dim: int, page_size: int) -> tuple:
     """Where a step keeps the work lists of one kind of attention layer in `ctx.memo`.  Layers
     share lists only if everything the lists are cut for agrees: the window, the group, the
     number of kv heads and the head size (they set the chunk length) and the rows of a prefill tile."""
-    rows = 128 if self._prefill_uses_tcgen05(head_dim, group, page_size) else (self.prefill_rows or 64)
-    return ("attention_plan", window, group, num_kv_heads, head_dim, rows)
+    return ("attention_plan", window, group, num_kv_heads, head_dim, self._prefill_rows(head_dim, group, page_size))
 
   def attention_graph_plan(self, *, window: int | None, num_heads: int, num_kv_heads: int, head_dim: int,
                            batch: int, bucket: int, max_burst: int, page_size: int):
@@ -700,13 +721,20 @@ class CudaOps:
     out = self._new(t, num_heads * head_dim, dtype=q.dtype)
     group = num_heads // num_kv_heads
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
-      prefill, decode, _, prefill_tc = self._attention_lib(head_dim)
+      prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)
       use_tc = prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
-      plan = self._attention_plan(ctx, window, group, 128 if use_tc else 0, num_kv_heads, head_dim)
+      use_pair = prefill_pair is not None and self._prefill_uses_pairs(head_dim, group, ctx.page_size)
+      plan = self._attention_plan(ctx, window, group, 256 if use_pair else (128 if use_tc else 0), num_kv_heads, head_dim)
       common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
                 _ptr(ctx.q_start))
       sizes = (num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window or 0))
-      if plan["num_prefill"] and use_tc:
+      if plan["num_prefill"] and use_pair:
+        rc = prefill_pair(*common, _ptr(out), t, *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
+                          _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_attn_prefill_pair: {_STATUS.get(rc, rc)}")
+      elif plan["num_prefill"] and use_tc:
         rc = prefill_tc(*common, _ptr(out), t, *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
                         _ptr(self.err), self._stream())
         self.launches += 1

@@ -477,16 +477,18 @@ def test_paged_attention_random(table, dtype, hq, hkv, dh, ps, window, cap):
   want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)
   # Prefill kernels: tcgen05 where the shape allows; mma.sync with tiles of 64 rows (two key groups),
   # 64 rows with a single key group (written 65 here) and 128 rows.
-  variants = [(False, 0)] if dtype == torch.float32 else [(True, 0), (False, 0), (False, 64), (False, 65), (False, 128)]
+  variants = [(False, 0)] if dtype == torch.float32 else [(True, 0), (True, 1), (False, 0), (False, 64), (False, 65), (False, 128)]
   for tc, rows in variants:
     ops.prefill_tcgen05 = tc
-    ops.prefill_rows = (64 if rows == 65 else rows) if rows >= hq // hkv else 0
+    ops.prefill_pairs = rows != 1  # (True, 1): tcgen05 by single blocks
+    ops.prefill_rows = (64 if rows == 65 else rows) if rows >= max(hq // hkv, 2) else 0
     ops.prefill_single_key_group = rows == 65
     sc.ctx.memo.clear()
     try:
       got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
     finally:
       ops.prefill_tcgen05 = True
+      ops.prefill_pairs = True
       ops.prefill_rows = 0
       ops.prefill_single_key_group = False
     ops.check_errors()
@@ -509,9 +511,13 @@ def test_tcgen05_prefill_long_walks(table, hq, hkv, dh, ps, window, cap):
                      device="cuda", ops=ops, seed=11)
   q = (torch.randn(sc.ctx.num_tokens, hq, dh) * 3.0).to(dtype).cuda()
   want = run_attention(ref, q, sc, hq, hkv, dh, cap, window)  # the plain statement
-  for _ in range(4):
+  for pairs in (True, False, True, False):  # by pairs of blocks where the shape allows, and by single blocks
+    ops.prefill_pairs = pairs
     sc.ctx.memo.clear()
-    got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+    try:
+      got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+    finally:
+      ops.prefill_pairs = True
     ops.check_errors()
     assert torch.isfinite(got).all()
     close(got, want, dtype, 2.0)
