@@ -175,11 +175,12 @@ class CudaOps:
     # does not take, the library's product and a pass of its own for the activation.  0: never.
     self.gated_tc_min_rows = int(os.environ.get("SIMPLY_B200_GATED_TC_MIN_ROWS", "129"))
     self.gated_tc_blocks = 0  # 0: one block per SM (tests: fewer, so that blocks walk many tiles)
-    # Blocks work in pairs (tcgen05 cta_group::2, tiles of 256 tokens) or each alone on tiles of 128.
-    # None: by the size of the product: measured at the Gemma 2 shapes, pairs are ahead (by 1 to
-    # 4 %) up to about 2e11 multiply-adds and single blocks (by 3 to 5 %) beyond, where the
-    # kernel runs long enough for the power limit to set the clocks.  True / False force one (tests).
-    self.gated_tc_pairs: bool | None = None
+    # Blocks work in pairs (tcgen05 cta_group::2, tiles of 256 tokens); False: each alone on tiles
+    # of 128 (tests).  Measured at the Gemma 2 shapes: in short bursts single blocks are ahead on
+    # the largest products (by 3 to 5 %), but whenever the GPU runs long enough for the power limit
+    # to set the clocks (a prefill step of the 27B shape is 90 ms) pairs, which move a third less
+    # data, are ahead at every size (by 2 to 4 %).
+    self.gated_tc_pairs = True
     self.mid_rows = {"qkv": 32, "gated": 32, "plain": 32, "head": 32}
     env = os.environ.get("SIMPLY_B200_SERVING_BATCH_PRODUCT")  # experiments: "qkv:128,gated:32,plain:0,head:128"
     if env:
@@ -568,9 +569,8 @@ class CudaOps:
     if (w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m >= self.gated_tc_min_rows > 0
         and x.is_contiguous() and w_gate_up.is_contiguous()):
       out = self._new(m, n // 2, dtype=torch.bfloat16)
-      pairs = self.gated_tc_pairs if self.gated_tc_pairs is not None else m * n * k <= 1.9e11
       if self._call("sb_gemm_gated_tc", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n // 2, k, activation,
-                    self.gated_tc_blocks, int(pairs), _ptr(self.err)) == 0:
+                    self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(self.err)) == 0:
         return out
     return self.gated_activation(self.linear(x, w_gate_up), activation)
 
