@@ -589,6 +589,56 @@ def test_paged_attention_one_key_stands_out(table, dtype, ps, window):
     sc.storage.copy_(backup)
 
 
+@pytest.mark.parametrize("hq,hkv,dh,ps", [(4, 4, 128, 64), (8, 2, 256, 128), (16, 2, 128, 64), (8, 4, 256, 64), (4, 2, 64, 16)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_prefill_attention_one_key_stands_out(table, hq, hkv, dh, ps, window):
+  """Portions of prompts (the prefill kernels: by pairs of blocks, by single blocks, mma.sync),
+  several groups and page sizes: one key matches every query far better than the rest and carries
+  a value of its own.  Placed at a tile's, a page's and the window's edge, and where a pair's first
+  block ends, it shows whether exactly the right keys are visible to exactly the right rows; the
+  whole result is compared with the plain statement as well."""
+  dtype = torch.bfloat16
+  ops, ref = table[dtype], ReferenceOps(dtype)
+  cap = 50.0
+  seqs = [(300, 330), (0, 257), (1000, 70)]
+  sc = make_scenario(seqs, num_kv_heads=hkv, head_dim=dh, window=window, page_size=ps, dtype=dtype,
+                     device="cuda", ops=ops, seed=13)
+  g = sc.manager.groups[0]
+  direction = torch.nn.functional.normalize(torch.randn(dh), dim=0)
+  q = (direction * 9.0).expand(sc.ctx.num_tokens, hq, dh).contiguous().to(dtype).cuda()
+  tokens_per_block = 128 // (hq // hkv)
+  for variant in ("pairs", "single", "mma"):
+    ops.prefill_pairs, ops.prefill_tcgen05 = variant == "pairs", variant != "mma"
+    try:
+      for spot in (0, 63, 64, 127, 128, 299, 300, 300 + tokens_per_block - 1, 300 + tokens_per_block, 430, 629, 1001):
+        backup = sc.storage.clone()
+        for slot, q_start, q_len in sc.seqs:
+          page = int(g.tables[slot, spot // ps]) if spot < q_start + q_len else -1
+          if page < 0:
+            continue  # given back (outside every window) or not yet there
+          sc.storage[page, 0, :, spot % ps, :] = (direction * 9.0).to(dtype).cuda()
+          sc.storage[page, 1, :, spot % ps, :] = 7.0
+        sc.ctx.memo.clear()
+        got = run_attention(ops, q, sc, hq, hkv, dh, cap, window)
+        ops.check_errors()
+        close(got, run_attention(ref, q, sc, hq, hkv, dh, cap, window), dtype, 2.0)
+        got = got.float().cpu().reshape(sc.ctx.num_tokens, hq, dh)
+        row = 0
+        for slot, q_start, q_len in sc.seqs:
+          for i in range(q_len):
+            pos = q_start + i
+            visible = spot <= pos and (window is None or pos - spot < window)
+            mean = got[row].mean().item()
+            if visible:
+              assert mean > 6.5, (variant, spot, pos, mean)
+            else:
+              assert abs(mean) < 1.0, (variant, spot, pos, mean)
+            row += 1
+        sc.storage.copy_(backup)
+    finally:
+      ops.prefill_pairs = ops.prefill_tcgen05 = True
+
+
 # ---- sampling ---------------------------------------------------------------------
 def test_sample_greedy_and_ties(table):
   ops = table[torch.float32]
