@@ -155,15 +155,17 @@ attn_prefill_pair_kernel(const PairParams p, const __grid_constant__ CUtensorMap
   cluster_sync_all();  // the other block's barriers and tensor memory exist before anything arrives there
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  // The kernel before this one writes the queries and the newest keys and values.
-  pdl_wait();
-  pdl_launch_dependents();
+  // The kernel before this one writes the queries and the newest keys and values: the producers
+  // wait for it before their first copy, and everything the other warps do follows from those
+  // copies (the set-up above ran beside that kernel's end).
 
   if (warp == 0 || warp == 2) {
     // ---- producers (one thread each, in both blocks): warp 0 brings Q and this block's half of the
     // key tiles, warp 2 its half of the value tiles.
     if (lane == 0) {
       const bool values = warp == 2;
+      pdl_wait();
+      pdl_launch_dependents();
       if (!values) {
         const uint32_t bar = mapa_shared(smem_u32(&q_full), 0);
         mbar_arrive_expect_tx_cluster(bar, Q_BYTES);
