@@ -8,7 +8,9 @@ decode steps that run back to back from CUDA graphs; the figure is the median of
 such bursts of K steps, each bracketed by events of its own (the last burst ends at the
 full context, the first 4 K tokens before it).  `e2e` is the same through the
 public entry point (`Engine.add_request` / `Engine.step`), host tokens in and out, one
-host round trip per step.  `prefill` is one 2,048-token prompt in one step; `points`
+host round trip per step.  `prefill` is one 2,048-token prompt in one step (the median of five
+such steps, each after a quarter of a second of rest: a prompt arrives on its own, and a GPU that
+has just run tens of milliseconds at full power is held back by its power limit); `points`
 holds decode at batch 1 and 64 (other presets: the batches their configuration names), at
 batch 8 with contexts of 1,024 and 4,096, and a serving-like run through `Engine.generate` (128
 requests over 64 slots, prompts of about 512 and outputs of about 128 tokens); `roofline`
@@ -548,6 +550,8 @@ def main(argv=None):
   for i in range(3 + 5):
     slot = engine.open_request(f"prefill{i}")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if i >= 3:
+      settle(torch, 0.25)  # a prompt arrives on its own: each timed step starts from settled clocks
     torch.cuda.synchronize()
     e0.record()
     engine.step_raw([StepEntry(slot, prompt, (p_tokens - 1,))])
