@@ -77,7 +77,7 @@ struct TcParams {
   int num_q_heads, num_kv_heads, page_size, num_pages;
   float cap;
   int window;
-  const int* items;  // (sequence, first token of the tile of 128 / G tokens)
+  const int* items;  // per block, in launch order: (sequence, first token of the tile of 128 / G tokens, kv head)
   int box_rows;      // rows per key/value TMA box: min(page_size, 64)
   int* err;
 };
@@ -114,7 +114,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
   __shared__ uint32_t tmem_slot;
   __shared__ int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = p.items[2 * blockIdx.x], i0 = p.items[2 * blockIdx.x + 1], m = blockIdx.y;
+  const int b = p.items[3 * blockIdx.x], i0 = p.items[3 * blockIdx.x + 1], m = p.items[3 * blockIdx.x + 2];
   const int group = p.num_q_heads / p.num_kv_heads;
   const int tokens_per_tile = BM / group;
   const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
@@ -522,7 +522,9 @@ static_assert(V_STAGES == 2, "the zeroing of value rows looks two tiles back");
 #define SB_FN(name) SB_CONCAT(SB_CONCAT(name, _hd), SB_HEAD_DIM)
 
 // Ragged prefill attention on tcgen05.  q: [T, Hq, DH]; cache: [pages, 2, Hkv, page_size, DH];
-// items: [num_items, 2] (sequence, first token of a tile of 128 / G tokens).  Returns -11 when
+// items: [num_items, 3] (sequence, first token of a tile of 128 / G tokens, kv head), in the order in
+// which the blocks are to start (longest walk first over all heads, so that the SMs that are free
+// first take the longest walks left).  Returns -11 when
 // the shapes do not allow it (the group must divide 128, the page size must be a power of two).
 extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const int* block_table, int max_pages,
                                          const int* cu_q, const int* q_start, void* out, int num_tokens,
@@ -558,7 +560,7 @@ extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  sb_launch(attn_prefill_tc_kernel, dim3(num_items, num_kv_heads), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv, map_out);
+  sb_launch(attn_prefill_tc_kernel, dim3(num_items), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv, map_out);
   SB_LAUNCH_CHECK();
   return 0;
 }

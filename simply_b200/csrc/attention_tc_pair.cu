@@ -78,7 +78,7 @@ struct PairParams {
   int num_q_heads, num_kv_heads, page_size, num_pages;
   float cap;
   int window;
-  const int* items;  // per pair: (sequence, first token of its 256 / G tokens)
+  const int* items;  // per pair, in launch order: (sequence, first token of its 256 / G tokens, kv head)
   int* err;
 };
 
@@ -113,8 +113,8 @@ attn_prefill_pair_kernel(const PairParams p, const __grid_constant__ CUtensorMap
   __shared__ int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = (int)cluster_ctarank();
-  const int pair = blockIdx.x >> 1, m = blockIdx.y;
-  const int b = p.items[2 * pair], i0_pair = p.items[2 * pair + 1];
+  const int pair = blockIdx.x >> 1;
+  const int b = p.items[3 * pair], i0_pair = p.items[3 * pair + 1], m = p.items[3 * pair + 2];
   const int group = p.num_q_heads / p.num_kv_heads;
   const int tokens_per_tile = BM / group;
   const int row0 = p.cu_q[b], q_len = p.cu_q[b + 1] - row0, qs = p.q_start[b];
@@ -474,7 +474,9 @@ attn_prefill_pair_kernel(const PairParams p, const __grid_constant__ CUtensorMap
 #define SB_FN(name) SB_CONCAT(SB_CONCAT(name, _hd), SB_HEAD_DIM)
 
 // Ragged prefill attention by pairs of blocks.  q: [T, Hq, DH]; cache: [pages, 2, Hkv, page_size, DH];
-// items: [num_pairs, 2] (sequence, first token of a pair's 256 / G tokens).  Returns -11 when the
+// items: [num_pairs, 3] (sequence, first token of a pair's 256 / G tokens, kv head), in the order
+// in which the pairs are to start: the GPU holds 74 pairs at once and gives the next one to the SMs
+// that finish first, so the order decides how evenly the walks fill them.  Returns -11 when the
 // shapes do not allow it (the group must divide 128; the page size must be a power of two of at
 // least 64).
 extern "C" int SB_FN(sb_attn_prefill_pair)(const void* q, const void* cache, const int* block_table, int max_pages,
@@ -513,7 +515,7 @@ extern "C" int SB_FN(sb_attn_prefill_pair)(const void* q, const void* cache, con
     configured = true;
   }
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)(2 * num_pairs), (unsigned)num_kv_heads);
+  config.gridDim = dim3((unsigned)(2 * num_pairs));
   config.blockDim = dim3(PAIR_THREADS);
   config.dynamicSmemBytes = PAIR_SMEM;
   config.stream = stream;

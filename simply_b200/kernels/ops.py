@@ -472,7 +472,15 @@ class CudaOps:
         first = max(int(q_start[b]) + i0 - window + 1, 0) if window else 0
         pre.append((last - first, int(b), i0))
     pre.sort(key=lambda x: -x[0])
-    prefill_items = np.array([(b, i0) for _, b, i0 in pre], dtype=np.int32).reshape(-1, 2)
+    if force_rows in (128, 256):
+      # The tcgen05 kernels' blocks, one per (tile of queries, kv head), longest walk first over all
+      # heads: the GPU holds 74 pairs (or 148 single blocks) at once and gives the next one in the list to the SMs that
+      # are free first, so this order fills them evenly (listed head by head, 128 blocks of a
+      # 4,096-token prompt ended as late as 53 tiles' time where 37 are enough).
+      prefill_items = np.array([(b, i0, m) for _, b, i0 in pre for m in range(num_kv_heads)],
+                               dtype=np.int32).reshape(-1, 3)
+    else:
+      prefill_items = np.array([(b, i0) for _, b, i0 in pre], dtype=np.int32).reshape(-1, 2)
     kv_hi = q_start + q_len
     kv_lo = np.maximum(q_start - window + 1, 0) if window else np.zeros_like(q_start)
     kv_lo = kv_lo // 64 * 64
