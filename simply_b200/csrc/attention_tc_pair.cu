@@ -453,7 +453,7 @@ attn_prefill_pair_kernel(const PairParams p, const __grid_constant__ CUtensorMap
       if (warp == 4 && lane == 0 && !s_failed) {
         for (int sl = 0; sl < SLABS; ++sl) tma_store_3d(&map_out, sq + sl * (BM * 128), sl * 64, m * group, row0 + i0);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();  // shared memory has been read; the grid's end covers the writes
       }
     }
     if (!ok) s_failed = 1;

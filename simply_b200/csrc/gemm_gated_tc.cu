@@ -247,7 +247,7 @@ gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
-    if (lane == 0) tma_store_wait_all();
+    if (lane == 0) tma_store_wait_read();  // shared memory has been read; the grid's end covers the writes
     if (!ok) s_failed = 1;
   }
   tc_fence_before_sync();
@@ -384,7 +384,7 @@ gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[buf]), 0));
     }
-    if (lane == 0) tma_store_wait_all();
+    if (lane == 0) tma_store_wait_read();  // shared memory has been read; the grid's end covers the writes
     if (!ok) s_failed = 1;
   }
   tc_fence_before_sync();
