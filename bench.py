@@ -12,7 +12,7 @@ host round trip per step.  `prefill` is one 2,048-token prompt in one step (the 
 such steps, each after a quarter of a second of rest: a prompt arrives on its own, and a GPU that
 has just run tens of milliseconds at full power is held back by its power limit); `points`
 holds decode at batch 1 and 64 (other presets: the batches their configuration names), at
-batch 8 with contexts of 1,024 and 4,096, and a serving-like run through `Engine.generate` (128
+batch 8 with contexts of 1,024 and 4,096, prompts of 4,096 and 8,192 tokens in one step, and a serving-like run through `Engine.generate` (128
 requests over 64 slots, prompts of about 512 and outputs of about 128 tokens); `roofline`
 relates the decode step's bytes (every weight once, plus the cache of the live requests) to the
 measured copy bandwidth; `kernels` gives the dominant kernels' own fractions, each timed alone
@@ -566,6 +566,28 @@ def main(argv=None):
              "frac": round(flops / (prefill_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)}
 
   if not args.skip_points:
+    # Longer prompts in one step each (attention's share grows with the length).
+    for tokens in (4096, 8192):
+      if tokens > context:
+        continue
+      long_prompt = rng.integers(0, cfg.vocab_size, tokens).tolist()
+      times = []
+      for i in range(1 + 3):
+        slot = engine.open_request(f"prefill{tokens}_{i}")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if i >= 1:
+          settle(torch, 0.25)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step_raw([StepEntry(slot, long_prompt, (tokens - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 1:
+          times.append(e0.elapsed_time(e1))
+        engine.close_request(slot)
+      ms = float(np.median(times))
+      points[f"prefill_{tokens}_ms"] = round(ms, 3)
+      points[f"prefill_{tokens}_frac"] = round(prefill_flops(cfg, layers, tokens) / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)
     budget = engine.scheduler.max_num_issue_tokens
     engine.scheduler.max_num_issue_tokens = 2048
     points.update(time_serving(engine, torch, cfg))
