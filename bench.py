@@ -544,7 +544,7 @@ def main(argv=None):
   # ---- prefill: one 2,048-token prompt in one step --------------------------------------
   rng = np.random.default_rng(5)
   p_tokens = min(2048, context)
-  prompt = rng.integers(0, cfg.vocab_size, p_tokens).tolist()
+  prompt = rng.integers(0, cfg.vocab_size, p_tokens).astype(np.int32)  # host tokens, as an array
   times = []
   settle(torch)
   for i in range(3 + 5):
@@ -570,7 +570,7 @@ def main(argv=None):
     for tokens in (4096, 8192):
       if tokens > context:
         continue
-      long_prompt = rng.integers(0, cfg.vocab_size, tokens).tolist()
+      long_prompt = rng.integers(0, cfg.vocab_size, tokens).astype(np.int32)
       times = []
       for i in range(1 + 3):
         slot = engine.open_request(f"prefill{tokens}_{i}")

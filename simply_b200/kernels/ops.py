@@ -157,6 +157,7 @@ class CudaOps:
     # ... and there by pairs of blocks (cta_group::2) where the shapes allow (head size 128 or 256,
     # pages of at least 64 tokens); False keeps single blocks (tests).
     self.prefill_pairs = True
+    self._rounded_scales: dict[float, float] = {}
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
     self.skinny_warps = 0
@@ -512,7 +513,10 @@ class CudaOps:
   def embed(self, table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
     if table.dtype == torch.bfloat16:
       # The reference rounds the constant to the activation dtype (simply/utils/module.py:477-481).
-      scale = float(torch.tensor(scale, dtype=torch.float32).to(torch.bfloat16))
+      rounded = self._rounded_scales.get(scale)
+      if rounded is None:
+        rounded = self._rounded_scales[scale] = float(torch.tensor(scale, dtype=torch.float32).to(torch.bfloat16))
+      scale = rounded
     out = self._new(ids.numel(), table.shape[1], dtype=torch.float32)
     self._call("sb_embed", _ptr(table), _code(table), _ptr(ids), float(scale), _ptr(out), ids.numel(),
                table.shape[1], table.shape[0], _ptr(self.err))
