@@ -415,13 +415,19 @@ def profile_step(engine, torch, cfg, args, context):
     step()
     entries = [StepEntry(e.slot, e.tokens, e.want) for e in entries]
   torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   torch.cuda.profiler.start()
+  t0 = time.perf_counter()
+  e0.record()
   step()
+  e1.record()
+  host_ms = (time.perf_counter() - t0) * 1e3
   torch.cuda.synchronize()
   torch.cuda.profiler.stop()
   engine.ops.check_errors()
   print(f"profiled one {args.profile} step: {len(entries)} entries, context {context}, "
-        f"{cfg.num_hidden_layers} layers")
+        f"{cfg.num_hidden_layers} layers; the host issued it in {host_ms:.2f} ms, the device took "
+        f"{e0.elapsed_time(e1):.2f} ms")
   return 0
 
 
